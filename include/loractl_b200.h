@@ -1,0 +1,208 @@
+/*
+ * loractl_b200 — C ABI of the B200 (sm_100a) quantized frozen-base LoRA linear.
+ *
+ * This is the boundary a `compute.backend: b200` arm of loractl-core binds to.
+ * Every entry point names the loractl-core item it replaces (paths are relative
+ * to the loractl repository root).  Conventions:
+ *
+ *   - all tensor pointers are DEVICE pointers on the device that was current
+ *     when the weight handle was created; the library never frees caller memory;
+ *   - `stream` is a `cudaStream_t` passed as `void*`; all work is stream-ordered,
+ *     nothing synchronises the device unless stated;
+ *   - every function returns an `lq_status`; on failure `lq_last_error()` holds
+ *     an actionable message for the calling thread.  Nothing aborts or traps, and
+ *     there is no CPU fallback: an unsupported request is an error;
+ *   - shapes use the reference's names: X is [N, K] (tokens x d_in), the frozen
+ *     weight is [M, K] in FILE layout (d_out x d_in, K contiguous, never
+ *     transposed — crates/loractl-core/src/mmdit.rs:404-412), LoRA A is [K, r],
+ *     LoRA B is [r, M] (burn Linear layout, crates/loractl-core/src/lora.rs:129-136),
+ *     s = alpha / rank.
+ */
+#ifndef LORACTL_B200_H
+#define LORACTL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LQ_ABI_VERSION 1
+
+typedef enum lq_status {
+    LQ_OK = 0,
+    LQ_ERR_INVALID = 1,     /* bad argument (the reference panics / bails here) */
+    LQ_ERR_CUDA = 2,        /* a CUDA runtime/driver call failed */
+    LQ_ERR_UNSUPPORTED = 3, /* valid request this build cannot run (never falls back) */
+    LQ_ERR_TIMEOUT = 4,     /* a bounded device-side wait gave up; context stays usable */
+    LQ_ERR_WORKSPACE = 5    /* caller workspace too small */
+} lq_status;
+
+/* Activation / output element type of one call.  LQ_F32 runs f32 arithmetic
+ * end to end (the reference's own precision on the quant path,
+ * crates/loractl-core/src/diffusion_trainer.rs:395-401); LQ_BF16 runs bf16
+ * operands with f32 accumulation on the tcgen05 tensor cores. */
+typedef enum lq_dtype { LQ_F32 = 0, LQ_BF16 = 1 } lq_dtype;
+
+/* Storage scheme of a frozen weight.  INT8/INT4 are crates/loractl-core/src/
+ * config.rs:637-649 `Quant::{Int8,Int4}` (symmetric, per-block f32 scale);
+ * FP8_E4M3 is the scaled-fp8 repack of crates/loractl-core/src/fp8.rs. */
+typedef enum lq_scheme { LQ_INT4 = 4, LQ_INT8 = 8, LQ_FP8_E4M3 = 108 } lq_scheme;
+
+/* How an fp8 `weight_scale` broadcasts (crates/loractl-core/src/fp8.rs:59-68). */
+typedef enum lq_scale_kind { LQ_SCALE_SCALAR = 0, LQ_SCALE_PER_CHANNEL = 1 } lq_scale_kind;
+
+/* Opaque frozen quantized weight: replaces the `QFloat` tensor(s) + bias held by
+ * `QuantLinear` (crates/loractl-core/src/mmdit.rs:413-428).  Immutable after
+ * creation except for lq_weight_set_bias; shareable across threads. */
+typedef struct lq_weight lq_weight_t;
+
+typedef struct lq_weight_info {
+    int64_t d_out;        /* M */
+    int64_t d_in;         /* K */
+    int32_t scheme;       /* lq_scheme */
+    int32_t group;        /* elements per scale block along K (0 for fp8) */
+    int32_t scale_kind;   /* lq_scale_kind (fp8 only) */
+    int32_t has_bias;
+    int32_t device;
+    int32_t reserved;
+    uint64_t packed_bytes; /* resident code bytes (padded, tile-contiguous) */
+    uint64_t scale_bytes;  /* resident scale bytes */
+} lq_weight_info;
+
+/* Message for the last failure on the calling thread ("" if none). */
+const char* lq_last_error(void);
+int lq_abi_version(void);
+
+/* ---- quantize / pack -------------------------------------------------------- */
+
+/* crates/loractl-core/src/quant.rs:102-117 `dequant_chunk_rows` — pure host
+ * function.  Writes at most `cap` row counts to `rows` and the chunk count to
+ * `n_chunks` (call with cap = 0 to size the array). */
+int lq_dequant_chunk_rows(uint64_t d_out, uint64_t d_in, uint64_t chunk_bytes,
+                          uint64_t* rows, size_t cap, size_t* n_chunks);
+
+/* crates/loractl-core/src/quant.rs:74-82 `quantize_linear_weight`: quantizes a
+ * device-resident [M, K] weight (w_dtype LQ_F32 or LQ_BF16, K contiguous) with the
+ * `quant_scheme` of quant.rs:61-67 — symmetric, one f32 scale per `group` elements
+ * along K, bits 4 (Q4S, clamp +-7) or 8 (Q8S, clamp +-127), rounding half away from
+ * zero.  `group` must be 32 (QUANT_BLOCK, quant.rs:52) or 64; K % group != 0 is
+ * LQ_ERR_INVALID (the reference asserts, quant.rs:76-80).  Allocates the handle's
+ * device storage (load-time path; not for the step loop). */
+int lq_quantize(const void* w, int w_dtype, int64_t d_out, int64_t d_in, int group, int bits,
+                void* stream, lq_weight_t** out);
+
+/* Builds a handle from already-quantized logical data: `codes` int8 [M, K] and
+ * `scales` f32 [M, K/group] on the device (the logical content of a burn QFloat
+ * tensor; used to join row chunks — crates/loractl-core/src/quant.rs:130-150 — and
+ * to load pre-quantized weights). */
+int lq_weight_from_codes(const int8_t* codes, const float* scales, int64_t d_out, int64_t d_in,
+                         int group, int bits, void* stream, lq_weight_t** out);
+
+/* crates/loractl-core/src/fp8.rs:279-329: wraps scaled-fp8 storage — `bytes` u8
+ * [M, K] e4m3fn (device), `scale` f32 scalar or [M] (device) — WITHOUT decoding it:
+ * the bytes stay fp8 in HBM and are decoded inside the kernels.  Copies both. */
+int lq_weight_from_fp8(const uint8_t* bytes, const float* scale, int scale_kind, int64_t d_out,
+                       int64_t d_in, void* stream, lq_weight_t** out);
+
+/* reference/fp8_reference.py:84-94 `quantize`: scale = amax/448 (>= 1e-12), scalar
+ * or per output row; q = e4m3fn(w / scale), round to nearest even.  `w` f32 [M, K]
+ * on the device. */
+int lq_fp8_quantize(const float* w, int64_t d_out, int64_t d_in, int per_channel, void* stream,
+                    lq_weight_t** out);
+
+/* `QuantLinear.bias` (crates/loractl-core/src/mmdit.rs:426-427): optional f32 [M],
+ * copied; NULL clears it. */
+int lq_weight_set_bias(lq_weight_t* w, const float* bias, void* stream);
+
+int lq_weight_info_get(const lq_weight_t* w, lq_weight_info* info);
+int lq_weight_destroy(lq_weight_t* w);
+
+/* Logical view of the packed storage, for bit-exactness checks independent of the
+ * tile layout: int4/int8 -> `codes` int8 [M, K], `scales` f32 [M, K/group];
+ * fp8 -> `codes` receives the raw e4m3 bytes, `scales` f32 [1] or [M]. */
+int lq_unpack(const lq_weight_t* w, int8_t* codes, float* scales, void* stream);
+
+/* `QuantLinear::dequantized_weight` (crates/loractl-core/src/mmdit.rs:435-444) /
+ * burn `dequantize`: the full [M, K] weight, `q * scale` (or `LUT[b] * scale`,
+ * crates/loractl-core/src/fp8.rs:305-317) computed in f32, stored as out_dtype. */
+int lq_dequantize(const lq_weight_t* w, void* out, int out_dtype, void* stream);
+
+/* ---- the hot path ----------------------------------------------------------- */
+
+/* Scratch the two calls below need for this (weight, N, rank, dtype); the caller
+ * owns the buffer (no hidden allocation in the step loop).  256-byte aligned. */
+size_t lq_linear_workspace_bytes(const lq_weight_t* w, int64_t n_tokens, int rank, int dtype);
+
+/* One LoRA'd quantized site, forward — `site()` at crates/loractl-core/src/
+ * mmdit.rs:526-536: BaseLinear::forward (mmdit.rs:483-519: x . dequant(wq)^T + bias)
+ * followed by LoraAdapters::apply (crates/loractl-core/src/adapters.rs:75-85) with
+ * LoraDelta::forward (crates/loractl-core/src/lora.rs:199-203):
+ *
+ *     Y[N,M] = X[N,K] . dequant(W)[M,K]^T + bias[M] + s * (X . A[K,r]) . B[r,M]
+ *
+ * X, Y have element type `dtype`; A, B are f32 (trainable parameters stay f32).
+ * rank == 0 (A, B NULL) is exactly `QuantBackend::quant_matmul_t`
+ * (crates/loractl-core/src/quant.rs:172-178) plus bias.  `H_out` (f32 [N, r],
+ * may be NULL) receives H = X . A for the backward.  Dropout on the adapter input
+ * is not supported (p must be 0; the reference forbids it under recompute,
+ * crates/loractl-core/src/diffusion_trainer.rs:342-348). */
+int lq_linear_fwd(const lq_weight_t* w, const void* X, int64_t n_tokens, int dtype,
+                  const float* A, const float* B, int rank, float scaling,
+                  void* Y, float* H_out, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Backward of lq_linear_fwd — `QuantMatmulT::backward` (crates/loractl-core/src/
+ * quant.rs:221-235: dX = dY . dequant(wq), no gradient to the weight) plus the stock
+ * autodiff of the LoRA delta (restated in reference/lora_reference.py:103-123):
+ *
+ *     dH = s * dY . B^T      dX[N,K] = dY . dequant(W) + dH . A^T
+ *     dA[K,r] = X^T . dH     dB[r,M] = s * H^T . dY
+ *
+ * dY, X, dX have element type `dtype`; H is the f32 [N, r] saved by the forward
+ * (NULL: recomputed as X . A); dA, dB are f32 and are OVERWRITTEN unless
+ * `accumulate` is non-zero (then added to, for a flat gradient bucket).
+ * dX may be NULL (input needs no gradient); dA/dB may be NULL when rank == 0. */
+int lq_linear_bwd(const lq_weight_t* w, const void* dY, const void* X, const float* H,
+                  int64_t n_tokens, int dtype, const float* A, const float* B, int rank,
+                  float scaling, void* dX, float* dA, float* dB, int accumulate,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- diagnostics -------------------------------------------------------------- */
+
+/* Device-side waits in the kernels are bounded; one that gives up records a code in a
+ * per-device error word instead of hanging.  This call synchronises `stream`, returns
+ * LQ_ERR_TIMEOUT (and clears the word) if a kernel gave up since the last call, else
+ * LQ_OK.  It is the device-side half of the reference's "fail loudly" policy
+ * (crates/loractl-core/src/config.rs:503-512); a trainer calls it where the reference
+ * reads the loss back (crates/loractl-core/src/diffusion_trainer.rs:1675). */
+int lq_check_device_status(void* stream);
+
+/* Launch accounting for benchmarks — the counterpart of the reference's bench probes
+ * (crates/loractl-core/src/probe.rs:24-39 phase markers; crates/loractl-bench/src/lib.rs).
+ * lq_kernel_launch_count: kernels this library has launched in this process so far.
+ * lq_profile_enable(1): from now on every launch is bracketed by a CUDA event pair on its
+ * stream; lq_profile_collect synchronises the device and returns, per kernel class
+ * (lq_profile_kinds() of them, named by lq_profile_kind_name), the summed milliseconds and
+ * the number of timed launches since the last collect, then forgets them. */
+uint64_t lq_kernel_launch_count(void);
+int lq_profile_enable(int on);
+int lq_profile_kinds(void);
+const char* lq_profile_kind_name(int kind);
+int lq_profile_collect(double* ms_by_kind, uint64_t* launches_by_kind, int n_kinds);
+
+/* The bare tcgen05 contraction the hot path is built from, exposed for unit tests and
+ * roofline probes: C[Mg, Ng] = A . B^T + bias with bf16 operands and f32 accumulation.
+ * An operand is K-major ([rows, Kg], Kg contiguous; *_mn = 0) or MN-major ([Kg, rows], rows
+ * contiguous; *_mn = 1); ld* are row strides in elements.  block_n is 64, 128 or 256;
+ * splits > 1 needs c_dtype LQ_F32, block_n 64 and `partial_ws` of
+ * splits * Mg * roundup(Ng, 64) floats.  The reference has no counterpart: burn's
+ * `float_matmul` (crates/loractl-core/src/quant.rs:233,251) is the nearest equivalent. */
+int lq_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, int64_t ldb,
+                 void* C, int c_dtype, int64_t ldc, int64_t Mg, int64_t Ng, int64_t Kg,
+                 int block_n, int splits, float* partial_ws, const float* bias, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LORACTL_B200_H */

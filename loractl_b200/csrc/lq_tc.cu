@@ -1,0 +1,637 @@
+// tcgen05 GEMM kernel + the host orchestration of the bf16 LoRA-linear path.
+//
+// One persistent, warp-specialised kernel serves every contraction on the path:
+//
+//   C[Mg, Ng] = A[Mg, Kg] . B[Ng, Kg]^T          (bf16 operands, f32 accumulation in TMEM)
+//
+//   warp 0 : TMA producer   (cp.async.bulk.tensor 2-D tiles, 128-byte swizzle, no multicast)
+//   warp 1 : MMA issuer     (tcgen05.mma cta_group::1, 128 x BLOCK_N x 16 per instruction)
+//   warps 2-5 : epilogue    (tcgen05.ld from TMEM -> registers -> global)
+//
+// The K loop may continue into a second pair of tensor maps ("K extension").  That is how
+// the rank-r LoRA product is fused into the frozen GEMM: with A1 = s*H (N x r, zero padded to
+// 64) and B1 = B^T (M x r), the extra k-block adds s * H . B to the same TMEM accumulator
+// before the single epilogue; X is therefore read once by the frozen GEMM.
+//
+// Work items are (output tile, k-split); with splits > 1 the kernel writes f32 partial tiles
+// that a fixed-order second stage reduces (deterministic: no atomics anywhere).
+#include <mutex>
+#include <vector>
+
+#include "lq_prof.cuh"
+#include "lq_tc.cuh"
+#include "lq_umma.cuh"
+
+namespace {
+
+using namespace umma;
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kThreads = 192;
+
+struct GemmParams {
+    int Mg, Ng;
+    int kb0, kb1;
+    int m_tiles, n_tiles, splits;
+    void* C;
+    long long ldc, split_stride;
+    const float* bias;
+    int* status;
+};
+
+template <int BLOCK_N>
+struct Cfg {
+    static constexpr uint32_t A_BYTES = BM * BK * 2;
+    static constexpr uint32_t B_BYTES = BLOCK_N * BK * 2;
+    static constexpr int STAGES = (192 * 1024) / (A_BYTES + B_BYTES);
+    static constexpr uint32_t TMEM_COLS = BLOCK_N * 2 < 32 ? 32 : BLOCK_N * 2;  // 2 accumulator stages
+    static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void item_coords(const GemmParams& p, int item, int& m_tile, int& n_tile, int& z) {
+    const int tiles = p.m_tiles * p.n_tiles;
+    z = item / tiles;
+    int t = item - z * tiles;
+    constexpr int GROUP = 16;  // m-tiles per raster group: keeps a 16-tile band of A hot in L2
+    int per_group = GROUP * p.n_tiles;
+    int g = t / per_group;
+    int first_m = g * GROUP;
+    int gsize = min(GROUP, p.m_tiles - first_m);
+    int r = t - g * per_group;
+    m_tile = first_m + r % gsize;
+    n_tile = r / gsize;
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store8(OutT* dst, const float* v);
+template <>
+__device__ __forceinline__ void store8<float>(float* dst, const float* v) {
+    *(float4*)dst = make_float4(v[0], v[1], v[2], v[3]);
+    *(float4*)(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* dst, const float* v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
+    uint4 u;
+    u.x = *(uint32_t*)&a; u.y = *(uint32_t*)&b; u.z = *(uint32_t*)&c; u.w = *(uint32_t*)&d;
+    *(uint4*)dst = u;
+}
+
+template <int BLOCK_N, bool A_MN, bool B_MN, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
+                 const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1, GemmParams p) {
+    using C = Cfg<BLOCK_N>;
+    constexpr int STAGES = C::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + (size_t)STAGES * C::A_BYTES;
+    uint64_t* bars = (uint64_t*)(smem + (size_t)STAGES * (C::A_BYTES + C::B_BYTES));
+    uint64_t* full = bars;
+    uint64_t* empty = bars + STAGES;
+    uint64_t* tfull = bars + 2 * STAGES;
+    uint64_t* tempty = bars + 2 * STAGES + 2;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full[s]), 1);
+            mbar_init(smem_u32(&empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&tfull[a]), 1);
+            mbar_init(smem_u32(&tempty[a]), 128);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tmA0);
+        prefetch_tmap(&tmB0);
+        prefetch_tmap(&tmA1);
+        prefetch_tmap(&tmB1);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int kb_total = p.kb0 + p.kb1;
+    const int num_items = p.m_tiles * p.n_tiles * p.splits;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- TMA producer ----------------
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+                int m_tile, n_tile, z;
+                item_coords(p, item, m_tile, n_tile, z);
+                const int kb_begin = (int)(((long long)z * kb_total) / p.splits);
+                const int kb_end = (int)(((long long)(z + 1) * kb_total) / p.splits);
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
+                    if (!mbar_wait(smem_u32(&empty[s]), phase ^ 1u, abort_flag, p.status, 11)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(&full[s]);
+                    mbar_expect_tx(bar, C::A_BYTES + C::B_BYTES);
+                    const bool ext = kb >= p.kb0;
+                    const CUtensorMap* ma = ext ? &tmA1 : &tmA0;
+                    const CUtensorMap* mb = ext ? &tmB1 : &tmB0;
+                    const int kc = (ext ? kb - p.kb0 : kb) * BK;
+                    const uint32_t sa = smem_u32(smem_a + (size_t)s * C::A_BYTES);
+                    const uint32_t sb = smem_u32(smem_b + (size_t)s * C::B_BYTES);
+                    if (!A_MN) {
+                        tma_load_2d(sa, ma, bar, kc, m_tile * BM);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * 8192, ma, bar, m_tile * BM + i * 64, kc);
+                    }
+                    if (!B_MN) {
+                        tma_load_2d(sb, mb, bar, kc, n_tile * BLOCK_N);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < BLOCK_N / 64; ++i)
+                            tma_load_2d(sb + i * 8192, mb, bar, n_tile * BLOCK_N + i * 64, kc);
+                    }
+                    if (++s == STAGES) { s = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // Give copies already in flight time to land before the CTA's shared memory is released.
+                for (int i = 0; i < 64; ++i) __nanosleep(1000);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---------------- MMA issuer ----------------
+            constexpr uint32_t idesc = make_idesc(1, 1, A_MN, B_MN, BM, BLOCK_N);
+            int s = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+                int m_tile, n_tile, z;
+                item_coords(p, item, m_tile, n_tile, z);
+                const int kb_begin = (int)(((long long)z * kb_total) / p.splits);
+                const int kb_end = (int)(((long long)(z + 1) * kb_total) / p.splits);
+                if (!mbar_wait(smem_u32(&tempty[acc]), acc_phase ^ 1u, abort_flag, p.status, 12)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BLOCK_N);
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
+                    if (!mbar_wait(smem_u32(&full[s]), phase, abort_flag, p.status, 13)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem_a + (size_t)s * C::A_BYTES);
+                    const uint32_t sb = smem_u32(smem_b + (size_t)s * C::B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        // K-major: 16 elements = 32 bytes along the row.  MN-major: 16 k-rows of 128 bytes.
+                        const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024)
+                                                 : make_smem_desc(sa + k * 32, 16, 1024);
+                        const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024)
+                                                 : make_smem_desc(sb + k * 32, 16, 1024);
+                        mma_f16(tmem_d, da, db, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+                    }
+                    mma_commit(smem_u32(&empty[s]));  // frees the smem stage once these MMAs retire
+                    if (++s == STAGES) { s = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                mma_commit(smem_u32(&tfull[acc]));  // accumulator complete -> epilogue
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5) ----------------
+        const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        OutT* Cbase = (OutT*)p.C;
+        for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+            int m_tile, n_tile, z;
+            item_coords(p, item, m_tile, n_tile, z);
+            if (!mbar_wait(smem_u32(&tfull[acc]), acc_phase, abort_flag, p.status, 14)) { ok = false; break; }
+            tc_fence_after();
+            const int row = m_tile * BM + quarter * 32 + lane;
+            OutT* crow = Cbase + (long long)z * p.split_stride + (long long)row * p.ldc;
+#pragma unroll 1
+            for (int c = 0; c < BLOCK_N / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N + c * 32), r);
+                tmem_ld_wait();
+                const int col0 = n_tile * BLOCK_N + c * 32;
+                if (row < p.Mg) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        const int col = col0 + j;
+                        if (col < p.Ng) {  // Ng % 8 == 0: an 8-column group is entirely in or out
+                            float v[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+                            if (p.bias) {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) v[e] += p.bias[col + e];
+                            }
+                            store8<OutT>(crow + col, v);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(smem_u32(&tempty[acc]));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ---- small elementwise helpers ----------------------------------------------------------
+
+// out[i * ldo + j] = bf16(alpha * in[i * si + j * sj]) for j < J, 0 for J <= j < Jpad.
+__global__ void __launch_bounds__(256) cast_pad_kernel(const float* __restrict__ in, long long si, long long sj,
+                                                       __nv_bfloat16* __restrict__ out, long long ldo, long long I,
+                                                       int J, int Jpad, float alpha) {
+    long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= I * Jpad) return;
+    long long i = idx / Jpad;
+    int j = (int)(idx - i * Jpad);
+    float v = j < J ? alpha * in[i * si + j * sj] : 0.f;
+    out[i * ldo + j] = __float2bfloat16(v);
+}
+
+// Second stage of a split contraction: sums `splits` f32 partial tiles in a fixed order.
+//   val = alpha * sum_z part[z][i][j]
+//   f32 out (optional): transposed ? out[j * ldo + i] : out[i * ldo + j]   (+= when accumulate)
+//   bf16 ext (optional): ext[i * ld_ext + j] = bf16(ext_scale * val), zero for J <= j < Jpad
+__global__ void __launch_bounds__(256) reduce_partials_kernel(const float* __restrict__ part, long long split_stride,
+                                                              int splits, long long ldp, long long I, int J, int Jpad,
+                                                              float alpha, float* __restrict__ out, long long ldo,
+                                                              int transposed, int accumulate,
+                                                              __nv_bfloat16* __restrict__ ext, long long ld_ext,
+                                                              float ext_scale) {
+    long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= I * Jpad) return;
+    long long i = idx / Jpad;
+    int j = (int)(idx - i * Jpad);
+    float v = 0.f;
+    if (j < J) {
+        for (int z = 0; z < splits; ++z) v += part[z * split_stride + i * ldp + j];
+        v *= alpha;
+        if (out) {
+            long long o = transposed ? (long long)j * ldo + i : i * ldo + j;
+            out[o] = accumulate ? out[o] + v : v;
+        }
+    }
+    if (ext) ext[i * ld_ext + j] = __float2bfloat16(j < J ? ext_scale * v : 0.f);
+}
+
+// ---- host side -------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)f;
+    });
+    if (!fn) throw LqError(LQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    return fn;
+}
+
+// 2-D bf16 tensor [rows, inner] with `ld` elements between rows; box = 64 x box_rows, 128-byte swizzle.
+CUtensorMap make_map(const void* base, int64_t inner, int64_t rows, int64_t ld, int box_rows) {
+    if (((uintptr_t)base & 15) != 0) throw LqError(LQ_ERR_INVALID, "tensor-core path: pointers must be 16-byte aligned");
+    if ((ld * 2) % 16 != 0) throw LqError(LQ_ERR_INVALID, "tensor-core path: row stride must be a multiple of 16 bytes");
+    CUtensorMap m;
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        throw LqError(LQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r));
+    return m;
+}
+
+struct DevCtx {
+    int sm_count = 0;
+    int* status = nullptr;
+};
+
+DevCtx& dev_ctx(int dev) {
+    static std::mutex mu;
+    static std::vector<DevCtx> ctx;
+    std::lock_guard<std::mutex> lk(mu);
+    if ((int)ctx.size() <= dev) ctx.resize(dev + 1);
+    DevCtx& c = ctx[dev];
+    if (!c.status) {
+        LQ_CUDA(cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        LQ_CUDA(cudaMalloc((void**)&c.status, sizeof(int)));
+        LQ_CUDA(cudaMemset(c.status, 0, sizeof(int)));
+    }
+    return c;
+}
+
+struct Operand {
+    const void* ptr;  // bf16
+    bool mn_major;    // false: [rows, Kg] (Kg contiguous); true: [Kg, rows] (rows contiguous)
+    int64_t ld;       // elements between consecutive rows of the stored matrix
+};
+
+template <int BLOCK_N, bool A_MN, bool B_MN, typename OutT>
+void launch_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand* a1, const Operand* b1, int64_t K1,
+                 OutT* Cout, int64_t ldc, int64_t split_stride, int64_t Mg, int64_t Ng, int splits, const float* bias,
+                 cudaStream_t st, int64_t b_rows = -1, int prof_kind = LQ_K_GEMM_MAIN) {
+    // b_rows: rows the B operand really has when fewer than Ng (TMA zero-fills the rest).
+    using C = Cfg<BLOCK_N>;
+    if (b_rows < 0) b_rows = Ng;
+    int dev;
+    LQ_CUDA(cudaGetDevice(&dev));
+    DevCtx& ctx = dev_ctx(dev);
+    auto mapA = [&](const Operand& o, int64_t Kg) {
+        return A_MN ? make_map(o.ptr, Mg, Kg, o.ld, 64) : make_map(o.ptr, Kg, Mg, o.ld, BM);
+    };
+    auto mapB = [&](const Operand& o, int64_t Kg) {
+        return B_MN ? make_map(o.ptr, b_rows, Kg, o.ld, 64) : make_map(o.ptr, Kg, b_rows, o.ld, BLOCK_N);
+    };
+    CUtensorMap tA0 = mapA(a0, K0), tB0 = mapB(b0, K0);
+    CUtensorMap tA1 = a1 ? mapA(*a1, K1) : tA0, tB1 = b1 ? mapB(*b1, K1) : tB0;
+    GemmParams p;
+    p.Mg = (int)Mg;
+    p.Ng = (int)Ng;
+    p.kb0 = (int)((K0 + BK - 1) / BK);
+    p.kb1 = a1 ? (int)((K1 + BK - 1) / BK) : 0;
+    p.m_tiles = (int)((Mg + BM - 1) / BM);
+    p.n_tiles = (int)((Ng + BLOCK_N - 1) / BLOCK_N);
+    p.splits = splits;
+    p.C = Cout;
+    p.ldc = ldc;
+    p.split_stride = split_stride;
+    p.bias = bias;
+    p.status = ctx.status;
+    long long items = (long long)p.m_tiles * p.n_tiles * splits;
+    int grid = (int)std::min<long long>(items, ctx.sm_count);
+    auto kern = umma_gemm_kernel<BLOCK_N, A_MN, B_MN, OutT>;
+    LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+    LqProf prof(prof_kind, st);
+    kern<<<grid, kThreads, C::SMEM, st>>>(tA0, tB0, tA1, tB1, p);
+    LQ_CUDA(cudaGetLastError());
+}
+
+int choose_splits(int64_t out_tiles, int64_t k_blocks, int sm_count) {
+    int64_t s = (2 * (int64_t)sm_count + out_tiles - 1) / out_tiles;
+    if (s > k_blocks) s = k_blocks;
+    if (s > 16) s = 16;
+    if (s < 1) s = 1;
+    return (int)s;
+}
+
+inline size_t al256(size_t x) { return (x + 255) & ~size_t(255); }
+inline int ext_width(int r) { return 64 * ((r + 63) / 64); }
+
+struct TcWs {
+    __nv_bfloat16* wscr;  // dequantized weight: [M, K] (fwd) or [K, M] (bwd)
+    float* Hf;            // [N, r]
+    float* dHf;           // [N, r]
+    __nv_bfloat16* ext_a; // [N, EXT]  fwd: s*H      bwd: dH
+    __nv_bfloat16* ext_b; // [N, EXT]                bwd: s*H
+    __nv_bfloat16* pdown; // fwd: A^T [r, K]         bwd: B [r, M]
+    __nv_bfloat16* pext;  // fwd: B^T [M, EXT]       bwd: A [K, EXT]
+    float* part;          // split partials
+    size_t bytes;
+};
+
+TcWs carve_tc(const lq_weight* w, int64_t N, int r, void* base, int sm_count) {
+    const size_t M = (size_t)w->M, K = (size_t)w->K;
+    const size_t EXT = (size_t)ext_width(r > 0 ? r : 1);
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        size_t o = al256(off);
+        off = o + bytes;
+        return base ? (void*)((char*)base + o) : nullptr;
+    };
+    TcWs t{};
+    t.wscr = (__nv_bfloat16*)take(M * K * 2);
+    if (r > 0) {
+        t.Hf = (float*)take((size_t)N * r * 4);
+        t.dHf = (float*)take((size_t)N * r * 4);
+        t.ext_a = (__nv_bfloat16*)take((size_t)N * EXT * 2);
+        t.ext_b = (__nv_bfloat16*)take((size_t)N * EXT * 2);
+        t.pdown = (__nv_bfloat16*)take((size_t)r * std::max(M, K) * 2);
+        t.pext = (__nv_bfloat16*)take(std::max(M, K) * EXT * 2);
+        size_t rows = std::max((size_t)N, std::max(M, K));
+        (void)sm_count;
+        t.part = (float*)take((size_t)16 * rows * EXT * 4);
+    }
+    t.bytes = al256(off);
+    return t;
+}
+
+// Out[I, r] = alpha * Z[I, C] . P[r, C]^T  via split-K tcgen05 GEMM + fixed-order reduce.
+void skinny_down(const void* Z, int64_t I, int64_t Cdim, int64_t ldz, const __nv_bfloat16* P, int64_t ldp_in, int r,
+                 float alpha, float* out_f32, __nv_bfloat16* ext, float ext_scale, float* part, int sm_count,
+                 cudaStream_t st) {
+    const int EXT = ext_width(r);
+    const int64_t kb = (Cdim + BK - 1) / BK;
+    const int64_t m_tiles = (I + BM - 1) / BM, n_tiles = EXT / 64;
+    const int splits = choose_splits(m_tiles * n_tiles, kb, sm_count);
+    Operand a{Z, false, ldz}, b{P, false, ldp_in};
+    launch_gemm<64, false, false, float>(a, b, Cdim, nullptr, nullptr, 0, part, EXT, I * (int64_t)EXT, I, EXT, splits,
+                                         nullptr, st, r, LQ_K_GEMM_DOWN);
+    long long total = (long long)I * EXT;
+    LqProf prof(LQ_K_REDUCE, st);
+    reduce_partials_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(part, I * (long long)EXT, splits, EXT, I, r,
+                                                                          EXT, alpha, out_f32, r, 0, 0, ext, EXT,
+                                                                          ext_scale);
+    LQ_CUDA(cudaGetLastError());
+}
+
+// Out = alpha * Z[Nred, C]^T . T[Nred, EXT]  (reduction over rows), Out is [C, r] or transposed [r, C].
+void skinny_grad(const void* Z, int64_t Nred, int64_t Cdim, int64_t ldz, const __nv_bfloat16* T, int r, float alpha,
+                 float* out, int transposed, int accumulate, float* part, int sm_count, cudaStream_t st) {
+    const int EXT = ext_width(r);
+    const int64_t kb = (Nred + BK - 1) / BK;
+    const int64_t m_tiles = (Cdim + BM - 1) / BM, n_tiles = EXT / 64;
+    const int splits = choose_splits(m_tiles * n_tiles, kb, sm_count);
+    Operand a{Z, true, ldz}, b{T, true, (int64_t)EXT};
+    launch_gemm<64, true, true, float>(a, b, Nred, nullptr, nullptr, 0, part, EXT, Cdim * (int64_t)EXT, Cdim, EXT, splits,
+                                       nullptr, st, -1, LQ_K_GEMM_GRAD);
+    long long total = (long long)Cdim * EXT;
+    LqProf prof(LQ_K_REDUCE, st);
+    reduce_partials_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+        part, Cdim * (long long)EXT, splits, EXT, Cdim, r, EXT, alpha, out, transposed ? Cdim : r, transposed,
+        accumulate, nullptr, 0, 0.f);
+    LQ_CUDA(cudaGetLastError());
+}
+
+void cast_pad(const float* in, long long si, long long sj, __nv_bfloat16* out, long long ldo, long long I, int J,
+              int Jpad, float alpha, cudaStream_t st) {
+    long long total = I * Jpad;
+    if (total <= 0) return;
+    LqProf prof(LQ_K_PREP, st);
+    cast_pad_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(in, si, sj, out, ldo, I, J, Jpad, alpha);
+    LQ_CUDA(cudaGetLastError());
+}
+
+template <typename OutT>
+void main_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand* a1, const Operand* b1, int64_t K1,
+               OutT* Cout, int64_t ldc, int64_t Mg, int64_t Ng, const float* bias, int sm_count, cudaStream_t st) {
+    // 256-wide tiles unless they would leave a large part of the last wave idle.
+    const int64_t m_tiles = (Mg + BM - 1) / BM;
+    const int64_t t256 = m_tiles * ((Ng + 255) / 256), t128 = m_tiles * ((Ng + 127) / 128);
+    auto eff = [&](int64_t tiles) { return (double)tiles / (double)(((tiles + sm_count - 1) / sm_count) * sm_count); };
+    const bool use256 = Ng >= 256 && eff(t256) + 0.04 >= eff(t128);
+    if (use256)
+        launch_gemm<256, false, false, OutT>(a0, b0, K0, a1, b1, K1, Cout, ldc, 0, Mg, Ng, 1, bias, st);
+    else
+        launch_gemm<128, false, false, OutT>(a0, b0, K0, a1, b1, K1, Cout, ldc, 0, Mg, Ng, 1, bias, st);
+}
+
+}  // namespace
+
+bool lq_tc_supported(const lq_weight* w, int64_t n_tokens, int rank) {
+    (void)n_tokens;
+    (void)rank;
+    return w->K % 8 == 0 && w->M % 8 == 0 && w->K >= 8 && w->M >= 8;
+}
+
+size_t lq_tc_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank) {
+    return carve_tc(w, n_tokens, rank, nullptr, 148).bytes;
+}
+
+int lq_tc_read_status(int device, cudaStream_t st) {
+    DevCtx& c = dev_ctx(device);
+    int v = 0;
+    LQ_CUDA(cudaStreamSynchronize(st));
+    LQ_CUDA(cudaMemcpy(&v, c.status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v != 0) LQ_CUDA(cudaMemset(c.status, 0, sizeof(int)));
+    return v;
+}
+
+void lq_tc_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, const float* B, int r, float s, void* Y,
+               float* H_out, void* ws, size_t ws_bytes, cudaStream_t st) {
+    const int64_t M = w->M, K = w->K;
+    DevCtx& ctx = dev_ctx(w->device);
+    LQ_CHECK_ARG(ws != nullptr, "workspace is NULL");
+    LQ_CHECK_ARG(((uintptr_t)ws & 255) == 0, "workspace must be 256-byte aligned");
+    TcWs t = carve_tc(w, N, r, ws, ctx.sm_count);
+    if (t.bytes > ws_bytes)
+        throw LqError(LQ_ERR_WORKSPACE, "workspace too small: need " + std::to_string(t.bytes) + " bytes, got " +
+                                            std::to_string(ws_bytes));
+    // 1. frozen weight -> bf16 scratch [M, K] (rounds q*scale, resp. LUT*scale, once to bf16)
+    lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, st);
+    Operand a0{X, false, K}, b0{t.wscr, false, K};
+    if (r == 0) {
+        main_gemm<__nv_bfloat16>(a0, b0, K, nullptr, nullptr, 0, (__nv_bfloat16*)Y, M, N, M, w->bias, ctx.sm_count, st);
+        return;
+    }
+    const int EXT = ext_width(r);
+    // 2. H = X . A  (f32 [N, r] for the backward; bf16 s*H, zero padded, as the K extension)
+    cast_pad(A, 1, r, t.pdown, K, r, (int)K, (int)K, 1.f, st);  // A^T [r, K]
+    float* Hf = H_out ? H_out : t.Hf;
+    skinny_down(X, N, K, K, t.pdown, K, r, 1.f, Hf, t.ext_a, s, t.part, ctx.sm_count, st);
+    // 3. Y = [X | s*H] . [W | B^T]^T + bias
+    cast_pad(B, 1, M, t.pext, EXT, M, r, EXT, 1.f, st);  // B^T [M, EXT]
+    Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
+    main_gemm<__nv_bfloat16>(a0, b0, K, &a1, &b1, EXT, (__nv_bfloat16*)Y, M, N, M, w->bias, ctx.sm_count, st);
+}
+
+void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H, int64_t N, const float* A,
+               const float* B, int r, float s, void* dX, float* dA, float* dB, int accumulate, void* ws,
+               size_t ws_bytes, cudaStream_t st) {
+    const int64_t M = w->M, K = w->K;
+    DevCtx& ctx = dev_ctx(w->device);
+    LQ_CHECK_ARG(ws != nullptr, "workspace is NULL");
+    LQ_CHECK_ARG(((uintptr_t)ws & 255) == 0, "workspace must be 256-byte aligned");
+    TcWs t = carve_tc(w, N, r, ws, ctx.sm_count);
+    if (t.bytes > ws_bytes)
+        throw LqError(LQ_ERR_WORKSPACE, "workspace too small: need " + std::to_string(t.bytes) + " bytes, got " +
+                                            std::to_string(ws_bytes));
+    const int EXT = ext_width(r > 0 ? r : 1);
+    if (dX) lq_launch_dequant(w, t.wscr, LQ_BF16, M, 1, st);  // W^T [K, M]
+    Operand a0{dY, false, M}, b0{t.wscr, false, M};
+    if (r == 0) {
+        if (dX) main_gemm<__nv_bfloat16>(a0, b0, M, nullptr, nullptr, 0, (__nv_bfloat16*)dX, K, N, K, nullptr, ctx.sm_count, st);
+        return;
+    }
+    // dH = s * dY . B^T   (f32 [N, r]; bf16 copy as the K extension of the dX GEMM and as dA's operand)
+    cast_pad(B, M, 1, t.pdown, M, r, (int)M, (int)M, 1.f, st);  // B as bf16 [r, M]
+    skinny_down(dY, N, M, M, t.pdown, M, r, s, t.dHf, t.ext_a, 1.f, t.part, ctx.sm_count, st);
+    if (dX) {  // dX = [dY | dH] . [W^T | A]^T
+        cast_pad(A, r, 1, t.pext, EXT, K, r, EXT, 1.f, st);  // A [K, EXT]
+        Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
+        main_gemm<__nv_bfloat16>(a0, b0, M, &a1, &b1, EXT, (__nv_bfloat16*)dX, K, N, K, nullptr, ctx.sm_count, st);
+    }
+    if (dA)  // dA[K, r] = X^T . dH
+        skinny_grad(X, N, K, K, t.ext_a, r, 1.f, dA, 0, accumulate, t.part, ctx.sm_count, st);
+    if (dB) {  // dB[r, M] = (s*H)^T . dY
+        const float* Hsrc = H;
+        if (!Hsrc) {
+            cast_pad(A, 1, r, t.pdown, K, r, (int)K, (int)K, 1.f, st);
+            skinny_down(X, N, K, K, t.pdown, K, r, 1.f, t.Hf, t.ext_b, s, t.part, ctx.sm_count, st);
+        } else {
+            cast_pad(Hsrc, r, 1, t.ext_b, EXT, N, r, EXT, s, st);
+        }
+        skinny_grad(dY, N, M, M, t.ext_b, r, 1.f, dB, 1, accumulate, t.part, ctx.sm_count, st);
+    }
+}
+
+void lq_tc_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, int64_t ldb, void* Cout,
+                     int c_dtype, int64_t ldc, int64_t Mg, int64_t Ng, int64_t Kg, int block_n, int splits,
+                     float* partial_ws, const float* bias, cudaStream_t st) {
+    Operand a{A, a_mn != 0, lda}, b{B, b_mn != 0, ldb};
+    LQ_CHECK_ARG(Ng % 8 == 0 && ldc % 8 == 0, "gemm: Ng and ldc must be multiples of 8");
+    if (splits > 1) {
+        LQ_CHECK_ARG(c_dtype == LQ_F32 && partial_ws != nullptr && block_n == 64, "split gemm: f32 out, block_n 64");
+        int64_t ldp = ((Ng + 63) / 64) * 64;
+        if (a_mn && b_mn)
+            launch_gemm<64, true, true, float>(a, b, Kg, nullptr, nullptr, 0, partial_ws, ldp, Mg * ldp, Mg, Ng, splits, nullptr, st);
+        else if (!a_mn && !b_mn)
+            launch_gemm<64, false, false, float>(a, b, Kg, nullptr, nullptr, 0, partial_ws, ldp, Mg * ldp, Mg, Ng, splits, nullptr, st);
+        else
+            throw LqError(LQ_ERR_UNSUPPORTED, "split gemm: mixed operand majors are not built");
+        long long total = (long long)Mg * ldp;
+        LqProf prof(LQ_K_REDUCE, st);
+        reduce_partials_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(partial_ws, Mg * ldp, splits, ldp, Mg, (int)Ng,
+                                                                              (int)ldp, 1.f, (float*)Cout, ldc, 0, 0, nullptr, 0, 0.f);
+        LQ_CUDA(cudaGetLastError());
+        return;
+    }
+#define LQ_GEMM_CASE(BN, AMN, BMN)                                                                                  \
+    if (block_n == BN && (a_mn != 0) == AMN && (b_mn != 0) == BMN) {                                                \
+        if (c_dtype == LQ_F32)                                                                                      \
+            launch_gemm<BN, AMN, BMN, float>(a, b, Kg, nullptr, nullptr, 0, (float*)Cout, ldc, 0, Mg, Ng, 1, bias, st); \
+        else                                                                                                        \
+            launch_gemm<BN, AMN, BMN, __nv_bfloat16>(a, b, Kg, nullptr, nullptr, 0, (__nv_bfloat16*)Cout, ldc, 0, Mg, Ng, 1, bias, st); \
+        return;                                                                                                     \
+    }
+    LQ_GEMM_CASE(256, false, false)
+    LQ_GEMM_CASE(128, false, false)
+    LQ_GEMM_CASE(64, false, false)
+    LQ_GEMM_CASE(64, true, true)
+    LQ_GEMM_CASE(128, false, true)
+    LQ_GEMM_CASE(128, true, false)
+#undef LQ_GEMM_CASE
+    throw LqError(LQ_ERR_UNSUPPORTED, "gemm: this (block_n, operand major) combination is not built");
+}

@@ -1,0 +1,24 @@
+// Tensor-core (tcgen05) path of the LoRA linear: host-side entry points.
+#pragma once
+
+#include "lq_internal.cuh"
+
+// True when the bf16 tcgen05 path can run this (weight, N, rank): TMA needs 16-byte row
+// strides, i.e. d_in % 8 == 0 and d_out % 8 == 0.
+bool lq_tc_supported(const lq_weight* w, int64_t n_tokens, int rank);
+size_t lq_tc_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank);
+
+void lq_tc_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, const float* B, int r, float s, void* Y,
+               float* H_out, void* ws, size_t ws_bytes, cudaStream_t st);
+void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H, int64_t N, const float* A,
+               const float* B, int r, float s, void* dX, float* dA, float* dB, int accumulate, void* ws,
+               size_t ws_bytes, cudaStream_t st);
+
+// Plain bf16 GEMM entry used by tests and probes: C[Mg,Ng] = A . B^T with either operand
+// K-major ([rows, Kg], Kg contiguous) or MN-major ([Kg, rows], rows contiguous).
+void lq_tc_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, int64_t ldb, void* C, int c_dtype,
+                     int64_t ldc, int64_t Mg, int64_t Ng, int64_t Kg, int block_n, int splits, float* partial_ws,
+                     const float* bias, cudaStream_t st);
+
+// Per-device error word written by kernels whose bounded waits gave up.  Synchronises `st`.
+int lq_tc_read_status(int device, cudaStream_t st);

@@ -1,0 +1,138 @@
+"""Quantized linear + the adapter attach seam — the mirror of
+crates/loractl-core/src/mmdit.rs:401-536 (`QuantLinear`, `BaseLinear`, `site`).
+
+Where the reference runs `base.forward(x)` and then `adapters.apply(...)` as separate
+tensor ops, a site whose base is quantized is ONE call into libloractl_b200 here
+(`lq_linear_fwd` / `lq_linear_bwd`): frozen GEMM, bias, rank-r delta and `alpha/rank`
+together, behind a `torch.autograd.Function`.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Union
+
+import torch
+from torch import nn
+
+from . import quant as Q
+from .adapters import LoraAdapters
+from .lora import LoraDelta
+
+
+class QuantLinear(nn.Module):
+    """crates/loractl-core/src/mmdit.rs:413-428.  `weight` is the frozen quantized weight in
+    file layout `[d_out, d_in]`; `rows` records the row-chunk layout the reference would
+    use (quant.rs:102-117) — here chunks are row ranges of one packed buffer, so the forward
+    is a single kernel whatever the layout.  `bias` stays f32."""
+
+    def __init__(self, weight: Union[Q.QuantWeight, List[Q.QuantWeight]], bias: Optional[torch.Tensor] = None):
+        super().__init__()
+        chunks = weight if isinstance(weight, list) else [weight]
+        self.rows = [c.d_out for c in chunks]
+        self.weight = Q.concat_chunks(chunks)
+        self.d_out, self.d_in = self.weight.d_out, self.weight.d_in
+        self.bias = None
+        if bias is not None:
+            self.bias = bias.detach().to(self.weight.device, torch.float32).contiguous()
+            self.weight.set_bias(self.bias)
+
+    @staticmethod
+    def from_linear(lin: nn.Linear, value: int, chunk_bytes: int = 0, block: int = Q.QUANT_BLOCK) -> "QuantLinear":
+        """`Mmdit::into_quantized_chunked` for one site (mmdit.rs:1134-1158,1266-1280).
+        torch's `nn.Linear.weight` is already `[d_out, d_in]`, so no transpose is needed."""
+        chunks = Q.quantize_linear_weight_chunked(lin.weight.detach(), value, chunk_bytes, block)
+        return QuantLinear(chunks, lin.bias.detach() if lin.bias is not None else None)
+
+    def dequantized_weight(self) -> torch.Tensor:
+        """mmdit.rs:435-444 — diagnostics only."""
+        return self.weight.dequantize()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return _fused(self.weight, x, None)
+
+
+class BaseLinear(nn.Module):
+    """crates/loractl-core/src/mmdit.rs:451-520: `Plain(Linear)` or `Quant(QuantLinear)`."""
+
+    def __init__(self, inner: nn.Module):
+        super().__init__()
+        self.inner = inner
+
+    @staticmethod
+    def plain(lin: nn.Linear) -> "BaseLinear":
+        return BaseLinear(lin)
+
+    @staticmethod
+    def quant(q: QuantLinear) -> "BaseLinear":
+        return BaseLinear(q)
+
+    @property
+    def is_quant(self) -> bool:
+        return isinstance(self.inner, QuantLinear)
+
+    @property
+    def d_in(self) -> int:
+        return self.inner.d_in if self.is_quant else self.inner.in_features
+
+    @property
+    def d_out(self) -> int:
+        return self.inner.d_out if self.is_quant else self.inner.out_features
+
+    def as_plain(self) -> nn.Linear:
+        if self.is_quant:
+            raise RuntimeError("BaseLinear::as_plain called on a quantized (Quant) site")
+        return self.inner
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.inner(x)
+
+
+class _LoraLinearFn(torch.autograd.Function):
+    """One LoRA'd quantized site.  Saves x and H = x.A for the backward; the frozen weight is
+    state (quant.rs:217-219), never a graph parent."""
+
+    @staticmethod
+    def forward(ctx, x2, a, b, wq, scaling):
+        y, h = Q.linear_fwd_raw(wq, x2, a, b, scaling)
+        ctx.wq, ctx.scaling = wq, scaling
+        ctx.save_for_backward(x2, h, a, b)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, h, a, b = ctx.saved_tensors
+        need_dx, need_da, need_db = ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.needs_input_grad[2]
+        dx, da, db = Q.linear_bwd_raw(ctx.wq, dy.contiguous(), x2, h, a, b, ctx.scaling,
+                                      need_dx=need_dx, need_da=need_da, need_db=need_db)
+        return dx, da, db, None, None
+
+
+def _fused(wq: Q.QuantWeight, x: torch.Tensor, delta: Optional[LoraDelta]) -> torch.Tensor:
+    """`BaseLinear::forward`'s Quant arm (mmdit.rs:487-519): flatten the leading dims to
+    `[n, d_in]`, run the op, reshape back with `d_out` last."""
+    if x.shape[-1] != wq.d_in:
+        raise ValueError(f"last dim {x.shape[-1]} != d_in {wq.d_in}")
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, wq.d_in).contiguous()
+    if delta is None:
+        y = Q._QuantMatmulT.apply(x2, wq)
+    else:
+        if delta.dropout > 0.0 and delta.training:
+            raise RuntimeError(
+                "lora.dropout > 0 is not supported on a quantized site of the b200 backend "
+                "(the fused kernel has no dropout; the reference also forbids it under recompute)")
+        y = _LoraLinearFn.apply(x2, delta.lora_a, delta.lora_b, wq, delta.scaling)
+    return y.reshape(*lead, wq.d_out)
+
+
+def apply_site(base: BaseLinear, delta: Optional[LoraDelta], x: torch.Tensor) -> torch.Tensor:
+    if base.is_quant:
+        return _fused(base.inner.weight, x, delta)
+    out = base(x)
+    return out if delta is None else out + delta(x)
+
+
+def site(adapters: Optional[LoraAdapters], path: str, base: BaseLinear, x: torch.Tensor) -> torch.Tensor:
+    """crates/loractl-core/src/mmdit.rs:526-536: run a base linear at an injectable site, adding
+    any adapter registered for `path`."""
+    delta = adapters.get(path) if adapters is not None else None
+    return apply_site(base, delta, x)

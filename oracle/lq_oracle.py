@@ -195,7 +195,7 @@ def encode_e4m3fn(x: np.ndarray) -> np.ndarray:
     dlo, dhi = ax - lo, hi - ax
     pick_hi = (dhi < dlo) | ((dhi == dlo) & ((idx % 2) == 0))  # ties -> even mantissa
     code = np.where(pick_hi, idx, idx - 1).astype(np.int64)
-    code = np.where(ax >= 464.0, 0x7F, code)  # halfway to the (absent) 480 rounds out of range
+    code = np.where(ax > 464.0, 0x7F, code)  # past the tie with the (absent) 480: out of range
     code = np.where(np.isnan(x), 0x7F, code)
     sign = np.signbit(x).astype(np.int64) << 7
     return (code | sign).astype(np.uint8)
