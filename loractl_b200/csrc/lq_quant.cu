@@ -5,6 +5,8 @@
 //   scale = absmax / qmax            (f32, IEEE division)
 //   q     = clamp(round(w / scale))  (f32 division, round half away from zero)
 // An all-zero block gets scale 0 and codes 0.
+#include <cuda_fp8.h>
+
 #include "lq_internal.cuh"
 #include "lq_prof.cuh"
 
@@ -158,6 +160,108 @@ __global__ void __launch_bounds__(256) dequant_kernel(LqWView w, OutT* __restric
     }
 }
 
+// Fast bf16 dequantisation for the GEMM scratch.  One block per 128 (m) x 64 (k) tile; every
+// thread produces 32 consecutive k of one row: f32 `q * scale` (resp. `LUT[b] * scale`) rounded
+// once to bf16.  transpose = 0 writes out[m * ld + k]; transpose = 1 stages the tile in shared
+// memory and writes out[k * ld + m] in 256-byte runs.  Requires ld % 8 == 0, 16-byte aligned
+// `out`, and for fp8 d_in % 16 == 0.
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *(uint32_t*)&v;
+}
+
+__global__ void __launch_bounds__(256) dequant_tile_kernel(LqWView w, __nv_bfloat16* __restrict__ out, int64_t ld,
+                                                           int transpose) {
+    constexpr int TLD = 136;  // staged tile row stride (bf16), keeps 16-byte alignment
+    __shared__ __align__(16) __nv_bfloat16 stage[64 * TLD];
+    const int t = threadIdx.x;
+    const int r = t >> 1, half = t & 1;
+    const int64_t mt = blockIdx.y, kt = blockIdx.x;
+    const int64_t m = mt * 128 + r, k0 = kt * 64 + half * 32;
+    uint32_t o[16];  // 32 bf16
+    const bool live = m < w.M && k0 < w.K;  // K % 32 == 0 on the int path, % 16 on fp8: handled below
+    if (!live) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = 0u;
+    } else if (w.scheme == LQ_INT4) {
+        const uint4 v = *((const uint4*)((const uint32_t*)w.packed + (mt * w.k_tiles + kt) * 1024) + t);
+        const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+        // the 32 k of this thread never straddle a scale group (group is 32 or 64, k0 % 32 == 0)
+        const float s = w.scales[(mt * w.n_groups + k0 / w.group) * 128 + r];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int q0 = (int)((words[c] >> (4 * j)) & 0xFu) - 8;
+                const int q1 = (int)((words[c] >> (4 * j + 16)) & 0xFu) - 8;
+                o[c * 4 + j] = pack_bf16x2((float)q0 * s, (float)q1 * s);
+            }
+        }
+    } else if (w.scheme == LQ_INT8) {
+        const uint4* src = (const uint4*)((const int8_t*)w.packed + (mt * w.k_tiles + kt) * 8192 + r * 64 + half * 32);
+        const float s = w.scales[(mt * w.n_groups + k0 / w.group) * 128 + r];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const uint4 v = src[c];
+            const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int q0 = (int)(int8_t)(words[j] & 0xFF), q1 = (int)(int8_t)((words[j] >> 8) & 0xFF);
+                const int q2 = (int)(int8_t)((words[j] >> 16) & 0xFF), q3 = (int)(int8_t)(words[j] >> 24);
+                o[c * 8 + j * 2] = pack_bf16x2((float)q0 * s, (float)q1 * s);
+                o[c * 8 + j * 2 + 1] = pack_bf16x2((float)q2 * s, (float)q3 * s);
+            }
+        }
+    } else {  // fp8 e4m3fn, row-major [M, K]
+        const float s = w.scale_kind == LQ_SCALE_PER_CHANNEL ? w.scales[m] : w.scales[0];
+        const uint8_t* row = (const uint8_t*)w.packed + m * w.K + k0;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            if (k0 + c * 16 < w.K) {
+                const uint4 v = *(const uint4*)(row + c * 16);
+                const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    // e4m3 -> f16 is exact (hardware cvt); NaN bytes stay NaN
+                    const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(words[j] & 0xFFFF), __NV_E4M3);
+                    const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(words[j] >> 16), __NV_E4M3);
+                    const float2 fl = __half22float2(*(const __half2*)&lo), fh = __half22float2(*(const __half2*)&hi);
+                    o[c * 8 + j * 2] = pack_bf16x2(fl.x * s, fl.y * s);
+                    o[c * 8 + j * 2 + 1] = pack_bf16x2(fh.x * s, fh.y * s);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[c * 8 + j] = 0u;
+            }
+        }
+    }
+    if (!transpose) {
+        if (live) {
+            uint4* dst = (uint4*)(out + m * ld + k0);
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                if (k0 + c * 8 < w.K) dst[c] = make_uint4(o[c * 4], o[c * 4 + 1], o[c * 4 + 2], o[c * 4 + 3]);
+        }
+        return;
+    }
+    // transposed: stage[k][m] then 256-byte rows out
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const __nv_bfloat162 v = *(const __nv_bfloat162*)&o[i];
+        stage[(half * 32 + 2 * i) * TLD + r] = v.x;
+        stage[(half * 32 + 2 * i + 1) * TLD + r] = v.y;
+    }
+    __syncthreads();
+    const int mc = (t & 15) * 8;  // 8 consecutive m per thread
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+        const int kk = pass * 16 + (t >> 4);
+        const int64_t k = kt * 64 + kk, mm = mt * 128 + mc;
+        if (k < w.K && mm < w.M)  // M % 8 == 0: an 8-wide group is entirely in or out
+            *(uint4*)(out + k * ld + mm) = *(const uint4*)&stage[kk * TLD + mc];
+    }
+}
+
 // ---- fp8 repack: scale = amax / 448 (>= 1e-12), q = e4m3fn(w / scale), RNE ------------
 
 __device__ __forceinline__ uint8_t encode_e4m3fn(float x) {
@@ -252,6 +356,14 @@ void lq_launch_unpack(const lq_weight* w, int8_t* codes, float* scales, cudaStre
 
 void lq_launch_dequant(const lq_weight* w, void* out, int out_dtype, int64_t ld, int transpose, cudaStream_t st) {
     LqProf prof(LQ_K_DEQUANT, st);
+    const bool aligned = (ld % 8 == 0) && (((uintptr_t)out & 15) == 0) && (w->M % 8 == 0) &&
+                         (w->scheme != LQ_FP8_E4M3 || w->K % 16 == 0);
+    if (out_dtype == LQ_BF16 && aligned) {
+        dim3 grid((unsigned)((w->K + 63) / 64), (unsigned)((w->M + 127) / 128));
+        dequant_tile_kernel<<<grid, 256, 0, st>>>(lq_view(w), (__nv_bfloat16*)out, ld, transpose);
+        LQ_CUDA(cudaGetLastError());
+        return;
+    }
     dim3 grid((unsigned)((w->K + 63) / 64), (unsigned)((w->M + 63) / 64));
     if (out_dtype == LQ_F32)
         dequant_kernel<float><<<grid, 256, 0, st>>>(lq_view(w), (float*)out, ld, transpose);

@@ -44,8 +44,9 @@ template <int BLOCK_N>
 struct Cfg {
     static constexpr uint32_t A_BYTES = BM * BK * 2;
     static constexpr uint32_t B_BYTES = BLOCK_N * BK * 2;
-    static constexpr int STAGES = (192 * 1024) / (A_BYTES + B_BYTES);
-    static constexpr uint32_t TMEM_COLS = BLOCK_N * 2 < 32 ? 32 : BLOCK_N * 2;  // 2 accumulator stages
+    static constexpr int STAGES = (208 * 1024) / (A_BYTES + B_BYTES);
+    // 2 accumulator stages; the allocation must be a power of two >= 32 columns
+    static constexpr uint32_t TMEM_COLS = BLOCK_N * 2 <= 128 ? 128 : (BLOCK_N * 2 <= 256 ? 256 : 512);
     static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
 };
 
@@ -497,15 +498,23 @@ void cast_pad(const float* in, long long si, long long sj, __nv_bfloat16* out, l
 template <typename OutT>
 void main_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand* a1, const Operand* b1, int64_t K1,
                OutT* Cout, int64_t ldc, int64_t Mg, int64_t Ng, const float* bias, int sm_count, cudaStream_t st) {
-    // 256-wide tiles unless they would leave a large part of the last wave idle.
+    // Tile width: 128 x 256 is the efficient shape (96 B/clk of operand traffic per SM); 128 x 128
+    // needs 128 B/clk and measured 1.5x slower per FLOP.  128 x 192 sits close to 256 and is taken
+    // when it fills the last wave of the persistent grid markedly better.
     const int64_t m_tiles = (Mg + BM - 1) / BM;
-    const int64_t t256 = m_tiles * ((Ng + 255) / 256), t128 = m_tiles * ((Ng + 127) / 128);
-    auto eff = [&](int64_t tiles) { return (double)tiles / (double)(((tiles + sm_count - 1) / sm_count) * sm_count); };
-    const bool use256 = Ng >= 256 && eff(t256) + 0.04 >= eff(t128);
-    if (use256)
-        launch_gemm<256, false, false, OutT>(a0, b0, K0, a1, b1, K1, Cout, ldc, 0, Mg, Ng, 1, bias, st);
-    else
+    auto waves_eff = [&](int bn) {
+        const int64_t tiles = m_tiles * ((Ng + bn - 1) / bn);
+        const int64_t rounds = (tiles + sm_count - 1) / sm_count;
+        const double pad = (double)Ng / (double)(((Ng + bn - 1) / bn) * bn);
+        return pad * (double)tiles / (double)(rounds * sm_count);
+    };
+    if (Ng <= 128) {
         launch_gemm<128, false, false, OutT>(a0, b0, K0, a1, b1, K1, Cout, ldc, 0, Mg, Ng, 1, bias, st);
+    } else if (Ng > 192 && waves_eff(256) >= 0.95 * waves_eff(192)) {
+        launch_gemm<256, false, false, OutT>(a0, b0, K0, a1, b1, K1, Cout, ldc, 0, Mg, Ng, 1, bias, st);
+    } else {
+        launch_gemm<192, false, false, OutT>(a0, b0, K0, a1, b1, K1, Cout, ldc, 0, Mg, Ng, 1, bias, st);
+    }
 }
 
 }  // namespace
@@ -627,6 +636,7 @@ void lq_tc_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B, int b_
         return;                                                                                                     \
     }
     LQ_GEMM_CASE(256, false, false)
+    LQ_GEMM_CASE(192, false, false)
     LQ_GEMM_CASE(128, false, false)
     LQ_GEMM_CASE(64, false, false)
     LQ_GEMM_CASE(64, true, true)

@@ -193,3 +193,26 @@ def test_fp8_encode_boundaries(golden_dir):
     b, s = wq.unpack()
     assert (s.cpu().numpy() == 1.0).all()
     assert np.array_equal(b.cpu().numpy(), O.encode_e4m3fn(xp))
+
+
+@pytest.mark.parametrize("scheme", ["int4", "int8", "fp8_scalar", "fp8_channel"])
+@pytest.mark.parametrize("shape", [(128, 64), (136, 96), (264, 320), (1024, 1024)])
+def test_bf16_dequantize_is_the_f32_value_rounded_once(scheme, shape):
+    """The GEMM scratch holds bf16(q * scale) resp. bf16(LUT[b] * scale): the f32 product of the
+    reference's dequantize (crates/loractl-core/src/quant.rs:232,250; src/fp8.rs:305-317) rounded
+    to nearest even once — bit-exact against the oracle's f32 value cast to bf16."""
+    m, k = shape
+    w = seeded(shape, 5, 0.02)
+    if scheme.startswith("int"):
+        bits = 4 if scheme == "int4" else 8
+        wq = lb().quantize_linear_weight(dev(w), bits, 32)
+        dq = O.dequantize(*O.quantize(w, 32, bits), 32)
+    else:
+        if k % 16:
+            pytest.skip("fp8 fast path needs d_in % 16 == 0")
+        pc = scheme == "fp8_channel"
+        wq = lb().fp8_quantize(dev(w), pc)
+        dq = O.fp8_dequant(*O.fp8_quantize(w, pc))
+    got = wq.dequantize(torch.bfloat16).cpu()
+    want = torch.from_numpy(dq).to(torch.bfloat16)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))

@@ -53,6 +53,8 @@ GEMM_CASES = [
     (256, 512, 256, 256, 0, 0, 1),
     (300, 520, 200, 256, 0, 0, 1),
     (300, 520, 200, 128, 0, 0, 1),
+    (300, 520, 200, 192, 0, 0, 1),
+    (1024, 3072, 512, 192, 0, 0, 1),
     (1000, 72, 512, 64, 0, 0, 1),
     (1000, 64, 1024, 64, 0, 0, 4),
     (4096, 3072, 3072, 256, 0, 0, 1),
