@@ -202,6 +202,29 @@ int lq_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, 
                  void* C, int c_dtype, int64_t ldc, int64_t Mg, int64_t Ng, int64_t Kg,
                  int block_n, int splits, float* partial_ws, const float* bias, void* stream);
 
+/* Split-K contraction that allocates nothing — it has no counterpart in the reference.
+ *
+ *     C[Mg, Ng] (f32, row stride ldc) = A . B^T      bf16 operands, f32 accumulation
+ *
+ * Same arithmetic as lq_gemm_bf16 with c_dtype LQ_F32, block_n 64 and `splits` k-ranges, but the
+ * caller passes no partial-sum workspace: the partial tiles live in a fixed 16 MiB array built
+ * into the library (one per GPU that loads it, held until the process exits).  It is meant for
+ * callers that cannot call cudaMalloc where they need the result — a stream that is being
+ * captured, an allocator callback, a loop whose memory was fixed at start-up.  The call itself
+ * performs no cudaMalloc / cudaFree and no other allocating device call.
+ *
+ * Both operands are K-major ([rows, Kg], operands_mn = 0) or both MN-major ([Kg, rows],
+ * operands_mn = 1); lda / ldb are their row strides in elements.
+ * Limit: splits * Mg * roundup(Ng, 64) must not exceed 4 * 2^20 floats, else LQ_ERR_WORKSPACE.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress) and
+ * the SM count; make that first call before any stream capture begins.
+ * Every call on a GPU shares the one array and it keeps the previous call's contents: calls that
+ * may overlap on the GPU (different streams without ordering) race and must be serialised by the
+ * caller.  If a bounded device-side wait gives up, every element of C is NaN. */
+int lq_gemm_bf16_splitk_static(const void* A, const void* B, int operands_mn, int64_t lda, int64_t ldb,
+                               float* C, int64_t ldc, int64_t Mg, int64_t Ng, int64_t Kg, int splits,
+                               void* stream);
+
 #ifdef __cplusplus
 }
 #endif

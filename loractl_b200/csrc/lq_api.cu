@@ -195,6 +195,9 @@ void bwd_simt(const lq_weight* w, const void* dY, const void* X, const float* H,
 
 }  // namespace
 
+// Lets entry points defined in other translation units report through lq_last_error().
+void lq_set_last_error(const std::string& msg) { g_last_error = msg; }
+
 // ---- exported symbols ---------------------------------------------------------------
 
 extern "C" {

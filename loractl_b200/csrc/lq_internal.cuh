@@ -154,3 +154,6 @@ struct LqSimtArgs {
     float alpha; int beta;
 };
 void lq_launch_simt_gemm(const LqSimtArgs& a, cudaStream_t st);
+
+// Sets the calling thread's lq_last_error() text (empty string clears it).
+void lq_set_last_error(const std::string& msg);

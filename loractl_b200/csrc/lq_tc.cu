@@ -645,3 +645,134 @@ void lq_tc_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B, int b_
 #undef LQ_GEMM_CASE
     throw LqError(LQ_ERR_UNSUPPORTED, "gemm: this (block_n, operand major) combination is not built");
 }
+
+// =========================================================================================
+// Split contraction for callers that must not allocate device memory
+// =========================================================================================
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they need a split-K
+// contraction: code running while a CUDA graph is being captured on the stream, code inside
+// a framework allocator's callback, or a real-time loop whose memory was fixed at start-up.
+// For them the partial tiles of the split live in a fixed array inside the library image
+// instead of in a caller workspace.  The array exists once per GPU that loads the library,
+// for the life of the process, and is shared by every call: two calls that can overlap on the
+// GPU (different streams) would overwrite each other's partials.
+namespace {
+
+constexpr size_t kStaticPartialFloats = size_t(4) << 20;  // 16 MiB of f32 partials per GPU
+static __device__ __align__(256) float g_static_partials[kStaticPartialFloats];
+static __device__ int g_static_status;  // wait-gave-up code of the current call, 0 = fine
+
+// Second stage for the static array: device code names the array directly.  Sums the splits
+// in a fixed order; if the first stage recorded a timed-out wait, the output is NaN instead.
+__global__ void __launch_bounds__(256) reduce_static_kernel(long long split_stride, int splits, long long ldp,
+                                                            long long I, int J, float* __restrict__ out,
+                                                            long long ldo) {
+    long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= I * J) return;
+    long long i = idx / J;
+    int j = (int)(idx - i * J);
+    float v = 0.f;
+    for (int z = 0; z < splits; ++z) v += g_static_partials[z * split_stride + i * ldp + j];
+    if (g_static_status != 0) v = __int_as_float(0x7FC00000);
+    out[i * ldo + j] = v;
+}
+
+struct StaticCtx {
+    float* partials = nullptr;  // device address of g_static_partials on this device
+    int* status = nullptr;      // device address of g_static_status on this device
+    int sm_count = 0;
+    bool ready = false;
+};
+
+// One-time set-up per device, with that device current.  In host code the array's name is
+// only a handle; cudaGetSymbolAddress turns it into the pointer a kernel can be given.
+StaticCtx& static_ctx(int dev) {
+    static std::mutex mu;
+    static std::vector<StaticCtx> ctx;
+    std::lock_guard<std::mutex> lk(mu);
+    if ((int)ctx.size() <= dev) ctx.resize(dev + 1);
+    StaticCtx& c = ctx[dev];
+    if (!c.ready) {
+        LQ_CUDA(cudaGetSymbolAddress((void**)&c.partials, g_static_partials));
+        LQ_CUDA(cudaGetSymbolAddress((void**)&c.status, g_static_status));
+        LQ_CUDA(cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        c.ready = true;
+    }
+    return c;
+}
+
+template <bool MN>
+void launch_static_split(const void* A, int64_t lda, const void* B, int64_t ldb, int64_t Mg, int64_t Ng, int64_t Kg,
+                         int splits, int64_t ldp, const StaticCtx& ctx, cudaStream_t st) {
+    using C = Cfg<64>;
+    CUtensorMap tA = MN ? make_map(A, Mg, Kg, lda, 64) : make_map(A, Kg, Mg, lda, BM);
+    CUtensorMap tB = MN ? make_map(B, Ng, Kg, ldb, 64) : make_map(B, Kg, Ng, ldb, 64);
+    GemmParams p;
+    p.Mg = (int)Mg;
+    p.Ng = (int)Ng;
+    p.kb0 = (int)((Kg + BK - 1) / BK);
+    p.kb1 = 0;
+    p.m_tiles = (int)((Mg + BM - 1) / BM);
+    p.n_tiles = (int)((Ng + 63) / 64);
+    p.splits = splits;
+    p.C = ctx.partials;
+    p.ldc = ldp;
+    p.split_stride = Mg * ldp;
+    p.bias = nullptr;
+    p.status = ctx.status;
+    long long items = (long long)p.m_tiles * p.n_tiles * splits;
+    int grid = (int)std::min<long long>(items, ctx.sm_count);
+    auto kern = umma_gemm_kernel<64, MN, MN, float>;
+    LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+    LqProf prof(LQ_K_GEMM_DOWN, st);
+    kern<<<grid, kThreads, C::SMEM, st>>>(tA, tB, tA, tB, p);
+    LQ_CUDA(cudaGetLastError());
+}
+
+}  // namespace
+
+extern "C" int lq_gemm_bf16_splitk_static(const void* A, const void* B, int operands_mn, int64_t lda, int64_t ldb,
+                                          float* Cout, int64_t ldc, int64_t Mg, int64_t Ng, int64_t Kg, int splits,
+                                          void* stream) {
+    try {
+        LQ_CHECK_ARG(A && B && Cout, "NULL operand");
+        LQ_CHECK_ARG(Mg > 0 && Ng > 0 && Kg > 0, "gemm dims must be positive");
+        LQ_CHECK_ARG(Ng % 8 == 0 && ldc >= Ng, "Ng must be a multiple of 8 and ldc >= Ng");
+        const int64_t kb = (Kg + BK - 1) / BK;
+        LQ_CHECK_ARG(splits >= 1 && splits <= 64 && splits <= kb, "splits must be in [1, min(64, ceil(Kg / 64))]");
+        const int64_t ldp = ((Ng + 63) / 64) * 64;
+        const unsigned long long need = (unsigned long long)splits * (unsigned long long)Mg * (unsigned long long)ldp;
+        if (need > kStaticPartialFloats)
+            throw LqError(LQ_ERR_WORKSPACE,
+                          "lq_gemm_bf16_splitk_static: splits * Mg * roundup(Ng, 64) = " + std::to_string(need) +
+                              " floats exceeds the built-in scratch of " + std::to_string(kStaticPartialFloats) +
+                              " floats (16 MiB); use lq_gemm_bf16 with a caller workspace");
+        int dev = 0;
+        LQ_CUDA(cudaGetDevice(&dev));
+        StaticCtx& ctx = static_ctx(dev);
+        cudaStream_t st = (cudaStream_t)stream;
+        // the error word must start at zero for this call; the partials need no clearing (every
+        // element the second stage reads is written by the first)
+        LQ_CUDA(cudaMemsetAsync(ctx.status, 0, sizeof(int), st));
+        if (operands_mn)
+            launch_static_split<true>(A, lda, B, ldb, Mg, Ng, Kg, splits, ldp, ctx, st);
+        else
+            launch_static_split<false>(A, lda, B, ldb, Mg, Ng, Kg, splits, ldp, ctx, st);
+        const long long total = (long long)Mg * Ng;
+        {
+            LqProf prof(LQ_K_REDUCE, st);
+            reduce_static_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(Mg * ldp, splits, ldp, Mg, (int)Ng,
+                                                                                Cout, ldc);
+            LQ_CUDA(cudaGetLastError());
+        }
+        lq_set_last_error("");
+        return LQ_OK;
+    } catch (const LqError& e) {
+        lq_set_last_error(e.what());
+        return e.status;
+    } catch (const std::exception& e) {
+        lq_set_last_error(std::string("internal error: ") + e.what());
+        return LQ_ERR_INVALID;
+    }
+}
