@@ -40,6 +40,10 @@ WORKLOADS = {
     "cfg1": ("int4", 3072, 3072, 16, 16.0, 4096, 64),
 }
 METRIC = "LoRA-linear fwd+bwd TFLOP/s"
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of the dominant kernel, from
+# the ncu capture summarised in profiles/umma_gemm_cfg2_step.md: forward 528.3 MB, backward
+# 872.5 MB, averaged like `achieved` is over the two launches of a step.
+NCU_TRAFFIC_BYTES = {"cfg2": (528.35e6 + 872.54e6) / 2}
 
 
 def step_flops(n, k, m, r):
@@ -297,7 +301,9 @@ def run_ours(args):
         roofline = {
             "bound": "tensor", "kernel": "umma_gemm_kernel (frozen GEMM + fused LoRA K extension)",
             "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": (achieved / peak) if achieved else None,
-            "peak_source": peak_src, "traffic": None,
+            "peak_source": peak_src, "traffic": NCU_TRAFFIC_BYTES.get(wl),
+            "traffic_unit": "bytes per launch (ncu, full-size launch)",
+            "algorithmic_bytes_per_launch": 2 * n * k + 2 * m * k + 2 * n * m,
             "launches_timed": gm_n, "avg_launch_ms": gm_ms / max(gm_n, 1),
             "share_of_step": gm_ms / total_ms if total_ms else None,
             "by_kernel_ms_per_step": {kk: v[0] / args.steps for kk, v in kinds.items() if v[1]},

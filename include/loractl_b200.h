@@ -168,6 +168,24 @@ int lq_linear_bwd(const lq_weight_t* w, const void* dY, const void* X, const flo
                   float scaling, void* dX, float* dA, float* dB, int accumulate,
                   void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- step glue on the flat LoRA buffers ---------------------------------------- */
+
+/* crates/loractl-core/src/diffusion_trainer.rs:1708-1725 (the finite check over every adapter
+ * gradient): clears the device int `flag`, then sets it to 1 if any of the `n` floats of the flat
+ * gradient buffer is NaN or Inf.  One kernel, no host synchronisation. */
+int lq_grad_nonfinite_flag(const float* grads, int64_t n, int* flag, void* stream);
+
+/* crates/loractl-core/src/diffusion_trainer.rs:1564-1566,1727-1728 (burn AdamW, decoupled decay)
+ * as one pass over flat f32 buffers of every adapter parameter:
+ *   p -= lr*wd*p;  m = b1 m + (1-b1) g;  v = b2 v + (1-b2) g^2;
+ *   p -= lr * (m / (1-b1^step)) / (sqrt(v / (1-b2^step)) + eps),   g = grad_scale * grads[i].
+ * `step` is the 1-based update count.  A non-zero device int at `skip_flag` (may be NULL) makes
+ * the call a no-op: the "skip the update" branch of the dynamic loss scale
+ * (diffusion_trainer.rs:1732-1742), taken on the device. */
+int lq_adamw_step(float* params, const float* grads, float* exp_avg, float* exp_avg_sq, int64_t n,
+                  float lr, float beta1, float beta2, float eps, float weight_decay, int64_t step,
+                  float grad_scale, const int* skip_flag, void* stream);
+
 /* ---- diagnostics -------------------------------------------------------------- */
 
 /* Device-side waits in the kernels are bounded; one that gives up records a code in a

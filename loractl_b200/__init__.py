@@ -11,6 +11,9 @@ from .adapters import LoraAdapters, LoraConfig, LoraSite, TargetSpec, build_adap
 from .linear import BaseLinear, QuantLinear, site
 from .fp8 import e4m3fn_lut, fp8_quantize, weight_from_fp8
 from .config import BackendKind, ComputeConfig, Precision, validate_b200
+from .optim import AdamW, DynamicLossScale, FlatAdapters, nonfinite_flag
+from .block_ckpt import checkpointed_step
+from . import dp
 
 __all__ = [
     "QUANT_BLOCK", "Quant", "QuantWeight", "check_device_status", "dequant_chunk_rows", "quant_matmul_t",
@@ -18,4 +21,5 @@ __all__ = [
     "LoraDelta", "LoraLinear", "init_factors", "LoraAdapters", "LoraConfig", "LoraSite", "TargetSpec",
     "build_adapters", "BaseLinear", "QuantLinear", "site", "e4m3fn_lut", "fp8_quantize", "weight_from_fp8",
     "BackendKind", "ComputeConfig", "Precision", "validate_b200",
+    "AdamW", "DynamicLossScale", "FlatAdapters", "nonfinite_flag", "checkpointed_step", "dp",
 ]

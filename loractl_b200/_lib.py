@@ -52,6 +52,8 @@ SIGNATURES = {
     "lq_linear_workspace_bytes": (_SZ, [_P, _I64, _I, _I]),
     "lq_linear_fwd": (_I, [_P, _P, _I64, _I, _P, _P, _I, _F, _P, _P, _P, _SZ, _P]),
     "lq_linear_bwd": (_I, [_P, _P, _P, _P, _I64, _I, _P, _P, _I, _F, _P, _P, _P, _I, _P, _SZ, _P]),
+    "lq_grad_nonfinite_flag": (_I, [_P, _I64, _P, _P]),
+    "lq_adamw_step": (_I, [_P, _P, _P, _P, _I64, _F, _F, _F, _F, _F, _I64, _F, _P, _P]),
     "lq_check_device_status": (_I, [_P]),
     "lq_kernel_launch_count": (C.c_uint64, []),
     "lq_profile_enable": (_I, [_I]),
