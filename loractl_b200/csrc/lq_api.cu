@@ -362,7 +362,9 @@ size_t lq_linear_workspace_bytes(const lq_weight_t* w, int64_t n_tokens, int ran
     if (!w || n_tokens < 0 || rank < 0) return 0;
     Carver c(nullptr, 0);
     if (dtype == LQ_BF16 && lq_tc_supported(w, n_tokens, rank)) {
-        return align256(lq_tc_workspace_bytes(w, n_tokens, rank)) + 256;
+        size_t need = lq_tc_workspace_bytes(w, n_tokens, rank);  // backward (and forward for N > 64)
+        if (lq_fused_supported(w, n_tokens, rank)) need = std::max(need, lq_fused_workspace_bytes(w, n_tokens, rank));
+        return align256(need) + 256;
     }
     c.take(sizeof(float) * (size_t)n_tokens * (size_t)(rank > 0 ? rank : 1));  // H
     c.take(sizeof(float) * (size_t)n_tokens * (size_t)(rank > 0 ? rank : 1));  // dH
@@ -378,6 +380,11 @@ int lq_linear_fwd(const lq_weight_t* w, const void* X, int64_t n_tokens, int dty
         if (n_tokens == 0) return;
         DeviceGuard dg(w->device);
         cudaStream_t st = (cudaStream_t)stream;
+        if (dtype == LQ_BF16 && lq_fused_supported(w, n_tokens, rank)) {
+            // packed-weight-stream regime: dequantise in shared memory, no bf16 weight in HBM
+            lq_fused_fwd(w, X, n_tokens, A, B, rank, scaling, Y, H_out, workspace, workspace_bytes, st);
+            return;
+        }
         if (dtype == LQ_BF16 && lq_tc_supported(w, n_tokens, rank)) {
             lq_tc_fwd(w, X, n_tokens, A, B, rank, scaling, Y, H_out, workspace, workspace_bytes, st);
             return;

@@ -1,0 +1,341 @@
+// Fused small-batch forward: the packed-weight-stream regime (N <= 64 tokens).
+//
+// At N <= 64 the frozen GEMM is bound by the HBM stream of the packed weight (int4: half a byte
+// per element), so the weight is read from HBM exactly once, as packed tiles, and dequantised in
+// shared memory on its way into tcgen05.mma — no bf16 copy of the weight ever exists in HBM.
+//
+//   roles swapped w.r.t. the large-N kernel: the weight tile is the 128-row MMA operand,
+//   the token tile is the narrow one:   D[128 features, NT tokens] += Wt[128, 64] . Xt[NT, 64]^T
+//
+//   warp 0      producer: cp.async.bulk of one packed tile (4 KB) + its scales, TMA tile of X
+//   warp 1      MMA issuer (tcgen05.mma 128 x NT x 16, f32 accumulator in TMEM)
+//   warps 2-9   dequant: nibbles -> exact bf16 integers (0x4300 | u is 128 + u; minus 136) times
+//               the group scale, written straight into the 128-byte-swizzled K-major operand
+//               layout (generic-proxy stores + fence.proxy.async); afterwards the same warps
+//               drain TMEM and store the item's partial tile
+//
+// Work items are (128-row weight tile, k-split); partial tiles are f32 and a second kernel sums
+// the splits in a fixed order and adds bias and the LoRA term s * (X.A) . B, so results are
+// deterministic.  Scale handling: w = bf16(q * bf16(scale)); q is exact, the scale is rounded to
+// bf16 once per group (relative 2^-9), inside the bf16 path's stated tolerance.
+#include <algorithm>
+
+#include "lq_prof.cuh"
+#include "lq_tc.cuh"
+#include "lq_umma.cuh"
+
+namespace {
+
+using namespace umma;
+
+constexpr int kFusedThreads = 320;
+constexpr int A_STAGES = 3;
+constexpr uint32_t A_BYTES = 128 * 64 * 2;  // dequantised operand tile
+
+struct FusedParams {
+    const uint8_t* packed;
+    const float* scales;
+    int M, N;
+    int k_tiles, n_groups, group;
+    int m_tiles, splits;
+    float* part;  // [splits][N][M]
+    int* status;
+};
+
+template <int NT>
+struct FCfg {
+    static constexpr uint32_t X_BYTES = NT * 128;
+    static constexpr uint32_t RAW_BYTES = X_BYTES + 4096 + 1024;  // X tile | packed tile | scales (2 groups max)
+    static constexpr int RAW_STAGES = ((208 * 1024 - A_STAGES * (int)A_BYTES) / (int)RAW_BYTES) > 16
+                                          ? 16
+                                          : ((208 * 1024 - A_STAGES * (int)A_BYTES) / (int)RAW_BYTES);
+    static constexpr uint32_t TMEM_COLS = NT * 2 < 32 ? 32 : NT * 2;
+    static constexpr size_t SMEM = (size_t)RAW_STAGES * RAW_BYTES + A_STAGES * A_BYTES + 1024 + 512;
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kFusedThreads, 1)
+fused_small_fwd_kernel(const __grid_constant__ CUtensorMap tmX, FusedParams p) {
+    using C = FCfg<NT>;
+    constexpr int RS = C::RAW_STAGES;
+    extern __shared__ uint8_t smem_raw_[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw_ + 1023) & ~(uintptr_t)1023);
+    uint8_t* raw = smem;                                   // RS x RAW_BYTES (each 1024-aligned)
+    uint8_t* abuf = smem + (size_t)RS * C::RAW_BYTES;      // A_STAGES x 16 KB
+    uint64_t* bars = (uint64_t*)(abuf + A_STAGES * A_BYTES);
+    uint64_t* full_raw = bars;
+    uint64_t* empty_raw = bars + RS;
+    uint64_t* full_a = bars + 2 * RS;
+    uint64_t* empty_a = full_a + A_STAGES;
+    uint64_t* tfull = empty_a + A_STAGES;
+    uint64_t* tempty = tfull + 2;
+    uint32_t* tmem_slot = (uint32_t*)(tempty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < RS; ++s) {
+            mbar_init(smem_u32(&full_raw[s]), 1);
+            mbar_init(smem_u32(&empty_raw[s]), 1);
+        }
+        for (int a = 0; a < A_STAGES; ++a) {
+            mbar_init(smem_u32(&full_a[a]), 256);
+            mbar_init(smem_u32(&empty_a[a]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&tfull[a]), 1);
+            mbar_init(smem_u32(&tempty[a]), 256);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tmX);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_items = p.m_tiles * p.splits;
+    const int groups_per_tile = 64 / p.group;  // 1 (G = 64) or 2 (G = 32)
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- producer ----------------
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+                const int mt = item / p.splits, z = item - mt * p.splits;
+                const int kt0 = (int)(((long long)z * p.k_tiles) / p.splits);
+                const int kt1 = (int)(((long long)(z + 1) * p.k_tiles) / p.splits);
+                for (int kt = kt0; kt < kt1; ++kt) {
+                    if (!mbar_wait(smem_u32(&empty_raw[s]), phase ^ 1u, abort_flag, p.status, 21)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(&full_raw[s]);
+                    const int g0 = kt * groups_per_tile;
+                    const int ng = min(groups_per_tile, p.n_groups - g0);  // a trailing half tile has one group
+                    const uint32_t sc_bytes = (uint32_t)ng * 512u;
+                    mbar_expect_tx(bar, C::X_BYTES + 4096u + sc_bytes);
+                    const uint32_t base = smem_u32(raw + (size_t)s * C::RAW_BYTES);
+                    tma_load_2d(base, &tmX, bar, kt * 64, 0);
+                    bulk_load(base + C::X_BYTES, p.packed + ((size_t)mt * p.k_tiles + kt) * 4096, 4096u, bar);
+                    bulk_load(base + C::X_BYTES + 4096u, p.scales + ((size_t)mt * p.n_groups + g0) * 128, sc_bytes, bar);
+                    if (++s == RS) { s = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok)
+                for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---------------- MMA issuer ----------------
+            constexpr uint32_t idesc = make_idesc(1, 1, false, false, 128, NT);
+            int s = 0, a = 0, acc = 0;
+            uint32_t phase = 0, aphase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+                const int mt = item / p.splits, z = item - mt * p.splits;
+                const int kt0 = (int)(((long long)z * p.k_tiles) / p.splits);
+                const int kt1 = (int)(((long long)(z + 1) * p.k_tiles) / p.splits);
+                if (!mbar_wait(smem_u32(&tempty[acc]), acc_phase ^ 1u, abort_flag, p.status, 22)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * NT);
+                for (int kt = kt0; kt < kt1; ++kt) {
+                    // the dequantised tile (its producers waited for the raw stage, X tile included)
+                    if (!mbar_wait(smem_u32(&full_a[a]), aphase, abort_flag, p.status, 23)) { ok = false; break; }
+                    if (!mbar_wait(smem_u32(&full_raw[s]), phase, abort_flag, p.status, 24)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(abuf + (size_t)a * A_BYTES);
+                    const uint32_t sx = smem_u32(raw + (size_t)s * C::RAW_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        mma_f16(tmem_d, make_smem_desc(sa + k * 32, 16, 1024), make_smem_desc(sx + k * 32, 16, 1024),
+                                idesc, (kt > kt0 || k > 0) ? 1u : 0u);
+                    mma_commit(smem_u32(&empty_a[a]));
+                    mma_commit(smem_u32(&empty_raw[s]));
+                    if (++s == RS) { s = 0; phase ^= 1u; }
+                    if (++a == A_STAGES) { a = 0; aphase ^= 1u; }
+                }
+                if (!ok) break;
+                mma_commit(smem_u32(&tfull[acc]));
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
+    } else {
+        // ---------------- dequant + epilogue (warps 2..9, 256 threads) ----------------
+        const int dt = threadIdx.x - 64;
+        const int r = dt >> 1, half = dt & 1;  // row of the tile, 32-k half of it
+        const int quarter = warp & 3;          // TMEM lane quarter of this warp
+        const int chalf = (warp - 2) >> 2;     // which half of the NT columns this warp drains
+        int s = 0, a = 0, acc = 0;
+        uint32_t phase = 0, aphase = 0, acc_phase = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+            const int mt = item / p.splits, z = item - mt * p.splits;
+            const int kt0 = (int)(((long long)z * p.k_tiles) / p.splits);
+            const int kt1 = (int)(((long long)(z + 1) * p.k_tiles) / p.splits);
+            for (int kt = kt0; kt < kt1; ++kt) {
+                if (!mbar_wait(smem_u32(&full_raw[s]), phase, abort_flag, p.status, 25)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&empty_a[a]), aphase ^ 1u, abort_flag, p.status, 26)) { ok = false; break; }
+                const uint8_t* st = raw + (size_t)s * C::RAW_BYTES + C::X_BYTES;
+                const uint4 v = *((const uint4*)st + dt);  // words 4dt..4dt+3: row r, chunks half*4..+3
+                const int g0 = kt * groups_per_tile;
+                const int gi = groups_per_tile == 2 ? half : 0;
+                float sc = 0.f;
+                if (g0 + gi < p.n_groups) sc = *((const float*)(st + 4096) + gi * 128 + r);
+                const __nv_bfloat162 s2 = __float2bfloat162_rn(sc);
+                const __nv_bfloat162 off = __float2bfloat162_rn(136.f);
+                const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+                uint8_t* arow = abuf + (size_t)a * A_BYTES + r * 128;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint32_t o[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t t = ((words[i] >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // (128+u_lo, 128+u_hi)
+                        __nv_bfloat162 q = __hsub2(*(__nv_bfloat162*)&t, off);            // exact integers -7..7
+                        __nv_bfloat162 wv = __hmul2(q, s2);
+                        o[j] = *(uint32_t*)&wv;
+                    }
+                    const int chunk = (half * 4 + i) ^ (r & 7);  // 128-byte swizzle of the operand layout
+                    *(uint4*)(arow + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(smem_u32(&full_a[a]));
+                if (++s == RS) { s = 0; phase ^= 1u; }
+                if (++a == A_STAGES) { a = 0; aphase ^= 1u; }
+            }
+            if (!ok) break;
+            // ---- epilogue of this item: D[m, n] -> part[z][n][m] ----
+            if (!mbar_wait(smem_u32(&tfull[acc]), acc_phase, abort_flag, p.status, 27)) { ok = false; break; }
+            tc_fence_after();
+            const int m = mt * 128 + quarter * 32 + lane;
+            float* pz = p.part + (size_t)z * p.N * p.M;
+#pragma unroll 1
+            for (int c = 0; c < NT / 2; c += 8) {
+                uint32_t rr[8];
+                const int col0 = chalf * (NT / 2) + c;
+                tmem_ld_x8(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * NT + col0), rr);
+                tmem_ld_wait();
+                if (m < p.M) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const int n = col0 + e;
+                        if (n < p.N) pz[(size_t)n * p.M + m] = __uint_as_float(rr[e]);
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(smem_u32(&tempty[acc]));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// Second stage: Y[n, m] = bf16( sum_z part[z][n][m] + bias[m] + s * sum_j H[n, j] * B[j, m] ).
+__global__ void __launch_bounds__(256) fused_finalize_kernel(const float* __restrict__ part, int splits, int N, int M,
+                                                             const float* __restrict__ bias,
+                                                             const float* __restrict__ H, const float* __restrict__ B,
+                                                             int r, float s, __nv_bfloat16* __restrict__ Y) {
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    const int n = blockIdx.y;
+    if (m >= M) return;
+    float v = 0.f;
+    for (int z = 0; z < splits; ++z) v += part[((size_t)z * N + n) * M + m];
+    if (bias) v += bias[m];
+    if (r > 0) {
+        float d = 0.f;
+        for (int j = 0; j < r; ++j) d = fmaf(H[(size_t)n * r + j], B[(size_t)j * M + m], d);
+        v += s * d;
+    }
+    Y[(size_t)n * M + m] = __float2bfloat16(v);
+}
+
+int pick_splits(int m_tiles, int k_tiles, int sms) {
+    int best = 1;
+    long long best_cost = -1;
+    for (int s = 1; s <= 16 && s <= k_tiles; ++s) {
+        long long waves = ((long long)m_tiles * s + sms - 1) / sms;
+        long long cost = waves * ((k_tiles + s - 1) / s) * 16 + s;  // tie-break: fewer splits (less partial traffic)
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
+    }
+    return best;
+}
+
+inline size_t al256(size_t x) { return (x + 255) & ~size_t(255); }
+
+template <int NT>
+void launch_fused(const CUtensorMap& tmX, const FusedParams& p, int grid, cudaStream_t st) {
+    auto kern = fused_small_fwd_kernel<NT>;
+    LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FCfg<NT>::SMEM));
+    LqProf prof(LQ_K_GEMM_MAIN, st);
+    kern<<<grid, kFusedThreads, FCfg<NT>::SMEM, st>>>(tmX, p);
+    LQ_CUDA(cudaGetLastError());
+}
+
+}  // namespace
+
+bool lq_fused_supported(const lq_weight* w, int64_t n_tokens, int rank) {
+    (void)rank;
+    return w->scheme == LQ_INT4 && n_tokens >= 1 && n_tokens <= 64 && w->K % 8 == 0 && w->M % 8 == 0;
+}
+
+size_t lq_fused_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank) {
+    size_t h = al256((size_t)n_tokens * (size_t)(rank > 0 ? rank : 1) * 4);
+    size_t part = al256((size_t)16 * (size_t)n_tokens * (size_t)w->M * 4);
+    return h + part + 256;
+}
+
+void lq_fused_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, const float* B, int r, float s,
+                  void* Y, float* H_out, void* ws, size_t ws_bytes, cudaStream_t st) {
+    LQ_CHECK_ARG(ws != nullptr && ((uintptr_t)ws & 255) == 0, "workspace must be non-NULL and 256-byte aligned");
+    if (lq_fused_workspace_bytes(w, N, r) > ws_bytes + 256)
+        throw LqError(LQ_ERR_WORKSPACE, "workspace too small for the fused small-batch path");
+    const int64_t M = w->M, K = w->K;
+    float* Hf = (float*)ws;
+    float* part = (float*)((char*)ws + al256((size_t)N * (size_t)(r > 0 ? r : 1) * 4));
+    if (r > 0) {  // H = X . A, f32 (a few MFLOP at N <= 64)
+        if (H_out) Hf = H_out;
+        LqSimtArgs h{};
+        h.A = X; h.a_dtype = LQ_BF16; h.sa_i = K; h.sa_k = 1;
+        h.b_mode = 0; h.Bp = A; h.b_dtype = LQ_F32; h.sb_k = r; h.sb_j = 1;
+        h.C = Hf; h.c_dtype = LQ_F32; h.ldc = r;
+        h.I = N; h.J = r; h.Kred = K; h.alpha = 1.f; h.beta = 0; h.bias = nullptr;
+        lq_launch_simt_gemm(h, st);
+    }
+    const int sms = lq_tc_sm_count(w->device);
+    FusedParams p;
+    p.packed = (const uint8_t*)w->packed;
+    p.scales = w->scales;
+    p.M = (int)M;
+    p.N = (int)N;
+    p.k_tiles = (int)w->k_tiles;
+    p.n_groups = (int)w->n_groups;
+    p.group = w->group;
+    p.m_tiles = (int)w->m_tiles;
+    p.splits = pick_splits(p.m_tiles, p.k_tiles, sms);
+    p.part = part;
+    p.status = lq_tc_status_word(w->device);
+    const int grid = std::min(p.m_tiles * p.splits, sms);
+    const int nt = N <= 16 ? 16 : (N <= 32 ? 32 : 64);
+    CUtensorMap tmX = lq_tc_make_map(X, K, N, K, nt);
+    if (nt == 16) launch_fused<16>(tmX, p, grid, st);
+    else if (nt == 32) launch_fused<32>(tmX, p, grid, st);
+    else launch_fused<64>(tmX, p, grid, st);
+    {
+        LqProf prof(LQ_K_REDUCE, st);
+        dim3 g((unsigned)((M + 255) / 256), (unsigned)N);
+        fused_finalize_kernel<<<g, 256, 0, st>>>(part, p.splits, (int)N, (int)M, w->bias, Hf, B, r, s, (__nv_bfloat16*)Y);
+        LQ_CUDA(cudaGetLastError());
+    }
+}

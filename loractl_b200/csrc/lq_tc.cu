@@ -519,6 +519,12 @@ void main_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand* 
 
 }  // namespace
 
+CUtensorMap lq_tc_make_map(const void* base, int64_t inner, int64_t rows, int64_t ld, int box_rows) {
+    return make_map(base, inner, rows, ld, box_rows);
+}
+int* lq_tc_status_word(int device) { return dev_ctx(device).status; }
+int lq_tc_sm_count(int device) { return dev_ctx(device).sm_count; }
+
 bool lq_tc_supported(const lq_weight* w, int64_t n_tokens, int rank) {
     (void)n_tokens;
     (void)rank;

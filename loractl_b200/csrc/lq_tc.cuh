@@ -1,6 +1,8 @@
 // Tensor-core (tcgen05) path of the LoRA linear: host-side entry points.
 #pragma once
 
+#include <cuda.h>
+
 #include "lq_internal.cuh"
 
 // True when the bf16 tcgen05 path can run this (weight, N, rank): TMA needs 16-byte row
@@ -22,3 +24,16 @@ void lq_tc_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B, int b_
 
 // Per-device error word written by kernels whose bounded waits gave up.  Synchronises `st`.
 int lq_tc_read_status(int device, cudaStream_t st);
+
+// Shared with the fused small-batch kernel (lq_fused.cu).
+// 2-D bf16 tensor map over [rows, inner] (ld elements between rows), box 64 x box_rows, 128-byte swizzle.
+CUtensorMap lq_tc_make_map(const void* base, int64_t inner, int64_t rows, int64_t ld, int box_rows);
+int* lq_tc_status_word(int device);
+int lq_tc_sm_count(int device);
+
+// Fused small-batch forward (N <= 64 tokens, int4 weights): the packed weight is streamed from HBM
+// exactly once and dequantised in shared memory on its way into tcgen05.mma.
+bool lq_fused_supported(const lq_weight* w, int64_t n_tokens, int rank);
+size_t lq_fused_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank);
+void lq_fused_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, const float* B, int r, float s,
+                  void* Y, float* H_out, void* ws, size_t ws_bytes, cudaStream_t st);
