@@ -261,6 +261,31 @@ __global__ void __launch_bounds__(256) fused_finalize_kernel(const float* __rest
     Y[(size_t)n * M + m] = __float2bfloat16(v);
 }
 
+// H[n, j] = sum_k X[n, k] * A[k, j] for one token per block.  256 threads = (256 / rp) k-slices x
+// rp columns; every slice accumulates its k range in f32, then the slices are summed in a fixed
+// order through shared memory (deterministic).  X is bf16, A and H are f32.
+__global__ void __launch_bounds__(256) small_h_kernel(const __nv_bfloat16* __restrict__ X, const float* __restrict__ A,
+                                                      int K, int r, int rp, float* __restrict__ H) {
+    __shared__ float red[256];
+    const int n = blockIdx.x;
+    const int j = threadIdx.x % rp, slice = threadIdx.x / rp, n_slices = 256 / rp;
+    const __nv_bfloat16* x = X + (size_t)n * K;
+    float acc = 0.f;
+    if (j < r) {
+        const int per = (K + n_slices - 1) / n_slices;
+        const int k0 = slice * per, k1 = min(K, k0 + per);
+#pragma unroll 8
+        for (int k = k0; k < k1; ++k) acc = fmaf(__bfloat162float(x[k]), A[(size_t)k * r + j], acc);
+    }
+    red[threadIdx.x] = acc;
+    __syncthreads();
+    if (slice == 0 && j < r) {
+        float h = 0.f;
+        for (int sidx = 0; sidx < n_slices; ++sidx) h += red[sidx * rp + j];
+        H[(size_t)n * r + j] = h;
+    }
+}
+
 int pick_splits(int m_tiles, int k_tiles, int sms) {
     int best = 1;
     long long best_cost = -1;
@@ -286,8 +311,7 @@ void launch_fused(const CUtensorMap& tmX, const FusedParams& p, int grid, cudaSt
 }  // namespace
 
 bool lq_fused_supported(const lq_weight* w, int64_t n_tokens, int rank) {
-    (void)rank;
-    return w->scheme == LQ_INT4 && n_tokens >= 1 && n_tokens <= 64 && w->K % 8 == 0 && w->M % 8 == 0;
+    return w->scheme == LQ_INT4 && n_tokens >= 1 && n_tokens <= 64 && w->K % 8 == 0 && w->M % 8 == 0 && rank <= 64;
 }
 
 size_t lq_fused_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank) {
@@ -304,14 +328,12 @@ void lq_fused_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, 
     const int64_t M = w->M, K = w->K;
     float* Hf = (float*)ws;
     float* part = (float*)((char*)ws + al256((size_t)N * (size_t)(r > 0 ? r : 1) * 4));
-    if (r > 0) {  // H = X . A, f32 (a few MFLOP at N <= 64)
+    if (r > 0) {  // H = X . A in f32: one block per token, a few MFLOP in total
         if (H_out) Hf = H_out;
-        LqSimtArgs h{};
-        h.A = X; h.a_dtype = LQ_BF16; h.sa_i = K; h.sa_k = 1;
-        h.b_mode = 0; h.Bp = A; h.b_dtype = LQ_F32; h.sb_k = r; h.sb_j = 1;
-        h.C = Hf; h.c_dtype = LQ_F32; h.ldc = r;
-        h.I = N; h.J = r; h.Kred = K; h.alpha = 1.f; h.beta = 0; h.bias = nullptr;
-        lq_launch_simt_gemm(h, st);
+        const int rp = r <= 16 ? 16 : (r <= 32 ? 32 : 64);
+        LqProf prof(LQ_K_GEMM_DOWN, st);
+        small_h_kernel<<<(unsigned)N, 256, 0, st>>>((const __nv_bfloat16*)X, A, (int)K, r, rp, Hf);
+        LQ_CUDA(cudaGetLastError());
     }
     const int sms = lq_tc_sm_count(w->device);
     FusedParams p;
