@@ -382,71 +382,82 @@ def run_stream(args):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     lib = L.lib()
-    k = m = 3072
-    r, s, sites = 16, 1.0, 40
-    g = torch.Generator(device=dev).manual_seed(5)
-    weights = []
-    for _ in range(sites):
-        w = torch.randn((m, k), generator=g, device=dev) * 0.02
-        weights.append(lb.quantize_linear_weight(w, 4, 64))
-    del w
-    a = torch.randn((k, r), generator=g, device=dev) / (k ** 0.5)
-    b = torch.randn((r, m), generator=g, device=dev) * 0.01
-    stream_bytes = k * m // 2 + 4 * k * m // 64
     peaks = {}
     if (ROOT / "MEASURED_PEAKS.json").exists():
         peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
     hbm = peaks.get("hbm_gbs", 6650.0)
-    results = {}
-    for n in (1, 8, 16, 64):
-        x = torch.randn((n, k), generator=g, device=dev).to(torch.bfloat16)
+    r, s = 16, 1.0
+    g = torch.Generator(device=dev).manual_seed(5)
+    all_results = {}
+    # (d_out, d_in, sites): config 1's 3072 x 3072 site, and the 3072 -> 12288 MLP up-projection
+    # of configs 3/5 held as int4 (21.2 MB of packed weight per site)
+    for m, k, sites in ((3072, 3072, 40), (12288, 3072, 10)):
+        weights = []
+        for _ in range(sites):
+            w = torch.randn((m, k), generator=g, device=dev) * 0.02
+            weights.append(lb.quantize_linear_weight(w, 4, 64))
+        del w
+        a = torch.randn((k, r), generator=g, device=dev) / (k ** 0.5)
+        b = torch.randn((r, m), generator=g, device=dev) * 0.01
+        stream_bytes = k * m // 2 + 4 * k * m // 64
+        results = {}
+        for n in (1, 8, 16, 64):
+            x = torch.randn((n, k), generator=g, device=dev).to(torch.bfloat16)
 
-        def chain():
-            y = None
-            for wq in weights:
-                y, _ = Q.linear_fwd_raw(wq, x, a, b, s, want_h=False)
-            return y
+            def chain():
+                y = None
+                for wq in weights:
+                    y, _ = Q.linear_fwd_raw(wq, x, a, b, s, want_h=False)
+                return y
 
-        for _ in range(3):
-            chain()
-        lb.check_device_status(dev)
-        # per-kernel-class time, eager launches (event pairs around every launch)
-        lib.lq_profile_enable(1)
-        lib.lq_profile_collect(None, None, 0)
-        for _ in range(3):
-            chain()
-        nk = lib.lq_profile_kinds()
-        ms_kind, cnt_kind = (C.c_double * nk)(), (C.c_uint64 * nk)()
-        lib.lq_profile_collect(ms_kind, cnt_kind, nk)
-        lib.lq_profile_enable(0)
-        kinds = {lib.lq_profile_kind_name(i).decode(): (ms_kind[i], int(cnt_kind[i])) for i in range(nk)}
-        fused_ms = kinds["gemm_main"][0] / max(kinds["gemm_main"][1], 1)
-        # whole-site time, graph replay
-        graph = torch.cuda.CUDAGraph()
-        side = torch.cuda.Stream(dev)
-        side.wait_stream(torch.cuda.current_stream(dev))
-        with torch.cuda.stream(side):
-            chain()
-            with torch.cuda.graph(graph, stream=side):
+            for _ in range(3):
                 chain()
-        torch.cuda.current_stream(dev).wait_stream(side)
-        for _ in range(3):
-            graph.replay()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = max(args.steps, 10)
-        e0.record()
-        for _ in range(reps):
-            graph.replay()
-        e1.record()
-        torch.cuda.synchronize()
-        site_ms = e0.elapsed_time(e1) / (reps * sites)
-        lb.check_device_status(dev)
-        results[str(n)] = {
-            "site_us": site_ms * 1e3, "site_stream_gbs": stream_bytes / (site_ms * 1e-3) / 1e9,
-            "fused_kernel_us": fused_ms * 1e3, "fused_kernel_stream_gbs": stream_bytes / (fused_ms * 1e-3) / 1e9,
-            "by_kernel_us": {kk: v[0] / max(v[1], 1) * 1e3 for kk, v in kinds.items() if v[1]},
-        }
+            lb.check_device_status(dev)
+            # per-kernel-class time, eager launches (event pairs around every launch)
+            lib.lq_profile_enable(1)
+            lib.lq_profile_collect(None, None, 0)
+            for _ in range(3):
+                chain()
+            nk = lib.lq_profile_kinds()
+            ms_kind, cnt_kind = (C.c_double * nk)(), (C.c_uint64 * nk)()
+            lib.lq_profile_collect(ms_kind, cnt_kind, nk)
+            lib.lq_profile_enable(0)
+            kinds = {lib.lq_profile_kind_name(i).decode(): (ms_kind[i], int(cnt_kind[i])) for i in range(nk)}
+            fused_ms = kinds["gemm_main"][0] / max(kinds["gemm_main"][1], 1)
+            # whole-site time, graph replay
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                chain()
+                with torch.cuda.graph(graph, stream=side):
+                    chain()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = max(args.steps, 10)
+            e0.record()
+            for _ in range(reps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            site_ms = e0.elapsed_time(e1) / (reps * sites)
+            lb.check_device_status(dev)
+            del graph
+            results[str(n)] = {
+                "site_us": site_ms * 1e3, "site_stream_gbs": stream_bytes / (site_ms * 1e-3) / 1e9,
+                "fused_kernel_us": fused_ms * 1e3,
+                "fused_kernel_stream_gbs": stream_bytes / (fused_ms * 1e-3) / 1e9,
+                "by_kernel_us": {kk: v[0] / max(v[1], 1) * 1e3 for kk, v in kinds.items() if v[1]},
+            }
+        all_results[f"{k}x{m}"] = {"stream_bytes_per_site": stream_bytes, "sites": sites, "by_tokens": results}
+        del weights
+    results = all_results["3072x3072"]["by_tokens"]
+    k = m = 3072
+    sites = 40
+    stream_bytes = all_results["3072x3072"]["stream_bytes_per_site"]
     best = results["64"]
     line = {
         "metric": "packed-weight stream GB/s (int4 3072x3072 forward, 64 tokens)", "value": best["site_stream_gbs"],
@@ -457,7 +468,7 @@ def run_stream(args):
         "roofline": {"bound": "hbm", "kernel": "fused_small_fwd_kernel", "achieved": best["fused_kernel_stream_gbs"],
                      "peak": hbm, "unit": "GB/s", "frac": best["fused_kernel_stream_gbs"] / hbm,
                      "algorithmic_bytes_per_launch": stream_bytes},
-        "by_tokens": results,
+        "by_site": all_results,
     }
     print(json.dumps(line))
 

@@ -28,7 +28,7 @@ namespace {
 
 using namespace umma;
 
-constexpr int kFusedThreads = 320;
+constexpr int kFusedThreads = 64 + 512;  // producer warp, MMA warp, two dequant groups of 8 warps
 constexpr int A_STAGES = 3;
 constexpr uint32_t A_BYTES = 128 * 64 * 2;  // dequantised operand tile
 
@@ -165,19 +165,25 @@ fused_small_fwd_kernel(const __grid_constant__ CUtensorMap tmX, FusedParams p) {
             }
         }
     } else {
-        // ---------------- dequant + epilogue (warps 2..9, 256 threads) ----------------
-        const int dt = threadIdx.x - 64;
+        // ---------------- dequant (warps 2..17: two groups of 256 threads) + epilogue (group 0) --------
+        // The groups take alternate k-tiles, so two tiles are converted concurrently; ring positions
+        // are derived from the running tile count, which both groups advance identically.
+        const int grp = (warp - 2) >> 3;
+        const int dt = (threadIdx.x - 64) & 255;
         const int r = dt >> 1, half = dt & 1;  // row of the tile, 32-k half of it
         const int quarter = warp & 3;          // TMEM lane quarter of this warp
-        const int chalf = (warp - 2) >> 2;     // which half of the NT columns this warp drains
-        int s = 0, a = 0, acc = 0;
-        uint32_t phase = 0, aphase = 0, acc_phase = 0;
+        const int chalf = ((warp - 2) >> 2) & 1;  // which half of the NT columns this warp drains
+        int acc = 0;
+        uint32_t acc_phase = 0, tix = 0;
         bool ok = true;
         for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
             const int mt = item / p.splits, z = item - mt * p.splits;
             const int kt0 = (int)(((long long)z * p.k_tiles) / p.splits);
             const int kt1 = (int)(((long long)(z + 1) * p.k_tiles) / p.splits);
-            for (int kt = kt0; kt < kt1; ++kt) {
+            for (int kt = kt0; kt < kt1; ++kt, ++tix) {
+                if ((int)(tix & 1u) != grp) continue;
+                const int s = (int)(tix % RS), a = (int)(tix % A_STAGES);
+                const uint32_t phase = (tix / RS) & 1u, aphase = (tix / A_STAGES) & 1u;
                 if (!mbar_wait(smem_u32(&full_raw[s]), phase, abort_flag, p.status, 25)) { ok = false; break; }
                 if (!mbar_wait(smem_u32(&empty_a[a]), aphase ^ 1u, abort_flag, p.status, 26)) { ok = false; break; }
                 const uint8_t* st = raw + (size_t)s * C::RAW_BYTES + C::X_BYTES;
@@ -205,11 +211,10 @@ fused_small_fwd_kernel(const __grid_constant__ CUtensorMap tmX, FusedParams p) {
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(smem_u32(&full_a[a]));
-                if (++s == RS) { s = 0; phase ^= 1u; }
-                if (++a == A_STAGES) { a = 0; aphase ^= 1u; }
             }
             if (!ok) break;
-            // ---- epilogue of this item: D[m, n] -> part[z][n][m] ----
+            if (grp != 0) continue;
+            // ---- epilogue of this item (group 0): D[m, n] -> part[z][n][m] ----
             if (!mbar_wait(smem_u32(&tfull[acc]), acc_phase, abort_flag, p.status, 27)) { ok = false; break; }
             tc_fence_after();
             const int m = mt * 128 + quarter * 32 + lane;
@@ -261,28 +266,52 @@ __global__ void __launch_bounds__(256) fused_finalize_kernel(const float* __rest
     Y[(size_t)n * M + m] = __float2bfloat16(v);
 }
 
-// H[n, j] = sum_k X[n, k] * A[k, j] for one token per block.  256 threads = (256 / rp) k-slices x
-// rp columns; every slice accumulates its k range in f32, then the slices are summed in a fixed
-// order through shared memory (deterministic).  X is bf16, A and H are f32.
+// H[n, j] = sum_k X[n, k] * A[k, j], one token per block, f32 accumulation (X bf16, A and H f32).
+// Thread t owns k = t, t + 256, ... and keeps RP partial sums in registers (rows of A are read as
+// float4, consecutive threads read consecutive rows); the 256 partial vectors are then combined by
+// a fixed shuffle tree and a fixed-order pass over the 8 warps, so the result is deterministic.
+template <int RP>
 __global__ void __launch_bounds__(256) small_h_kernel(const __nv_bfloat16* __restrict__ X, const float* __restrict__ A,
-                                                      int K, int r, int rp, float* __restrict__ H) {
-    __shared__ float red[256];
-    const int n = blockIdx.x;
-    const int j = threadIdx.x % rp, slice = threadIdx.x / rp, n_slices = 256 / rp;
+                                                      int K, int r, float* __restrict__ H) {
+    __shared__ float red[8][RP];
+    const int n = blockIdx.x, t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const __nv_bfloat16* x = X + (size_t)n * K;
-    float acc = 0.f;
-    if (j < r) {
-        const int per = (K + n_slices - 1) / n_slices;
-        const int k0 = slice * per, k1 = min(K, k0 + per);
-#pragma unroll 8
-        for (int k = k0; k < k1; ++k) acc = fmaf(__bfloat162float(x[k]), A[(size_t)k * r + j], acc);
+    float acc[RP];
+#pragma unroll
+    for (int j = 0; j < RP; ++j) acc[j] = 0.f;
+    const bool vec = (r == RP);  // rows of A are RP floats: 16-byte aligned float4 loads
+#pragma unroll 4
+    for (int k = t; k < K; k += 256) {
+        const float xv = __bfloat162float(x[k]);
+        const float* arow = A + (size_t)k * r;
+        if (vec) {
+#pragma unroll
+            for (int j = 0; j < RP; j += 4) {
+                const float4 a4 = *(const float4*)(arow + j);
+                acc[j] = fmaf(xv, a4.x, acc[j]);
+                acc[j + 1] = fmaf(xv, a4.y, acc[j + 1]);
+                acc[j + 2] = fmaf(xv, a4.z, acc[j + 2]);
+                acc[j + 3] = fmaf(xv, a4.w, acc[j + 3]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < RP; ++j)
+                if (j < r) acc[j] = fmaf(xv, arow[j], acc[j]);
+        }
     }
-    red[threadIdx.x] = acc;
+#pragma unroll
+    for (int j = 0; j < RP; ++j) {
+        float v = acc[j];
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (lane == 0) red[warp][j] = v;
+    }
     __syncthreads();
-    if (slice == 0 && j < r) {
+    if (t < r) {
         float h = 0.f;
-        for (int sidx = 0; sidx < n_slices; ++sidx) h += red[sidx * rp + j];
-        H[(size_t)n * r + j] = h;
+#pragma unroll
+        for (int w8 = 0; w8 < 8; ++w8) h += red[w8][t];
+        H[(size_t)n * r + t] = h;
     }
 }
 
@@ -330,9 +359,11 @@ void lq_fused_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, 
     float* part = (float*)((char*)ws + al256((size_t)N * (size_t)(r > 0 ? r : 1) * 4));
     if (r > 0) {  // H = X . A in f32: one block per token, a few MFLOP in total
         if (H_out) Hf = H_out;
-        const int rp = r <= 16 ? 16 : (r <= 32 ? 32 : 64);
         LqProf prof(LQ_K_GEMM_DOWN, st);
-        small_h_kernel<<<(unsigned)N, 256, 0, st>>>((const __nv_bfloat16*)X, A, (int)K, r, rp, Hf);
+        const __nv_bfloat16* Xb = (const __nv_bfloat16*)X;
+        if (r <= 16) small_h_kernel<16><<<(unsigned)N, 256, 0, st>>>(Xb, A, (int)K, r, Hf);
+        else if (r <= 32) small_h_kernel<32><<<(unsigned)N, 256, 0, st>>>(Xb, A, (int)K, r, Hf);
+        else small_h_kernel<64><<<(unsigned)N, 256, 0, st>>>(Xb, A, (int)K, r, Hf);
         LQ_CUDA(cudaGetLastError());
     }
     const int sms = lq_tc_sm_count(w->device);
