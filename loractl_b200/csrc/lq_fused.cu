@@ -42,17 +42,31 @@ struct FusedParams {
     int* status;
 };
 
+constexpr int KS = 4;  // k-tiles per pipeline stage: one bulk copy moves 4 packed tiles (16 KB)
+
 template <int NT>
 struct FCfg {
-    static constexpr uint32_t X_BYTES = NT * 128;
-    static constexpr uint32_t RAW_BYTES = X_BYTES + 4096 + 1024;  // X tile | packed tile | scales (2 groups max)
-    static constexpr int RAW_STAGES = ((208 * 1024 - A_STAGES * (int)A_BYTES) / (int)RAW_BYTES) > 16
-                                          ? 16
-                                          : ((208 * 1024 - A_STAGES * (int)A_BYTES) / (int)RAW_BYTES);
-    static constexpr uint32_t TMEM_COLS = NT * 2 < 32 ? 32 : NT * 2;
+    static constexpr uint32_t X_BYTES = NT * 128;                // one X tile [NT tokens][64 k] bf16
+    static constexpr uint32_t RAW_BYTES = KS * (X_BYTES + 4096 + 1024);  // X tiles | packed tiles | scales
+    static constexpr int RAW_STAGES = (208 * 1024 - A_STAGES * (int)A_BYTES) / (int)RAW_BYTES;
+    // 2 accumulator stages x 4 independent accumulators (one per 16-wide k-step of a tile): MMAs
+    // that accumulate into the same TMEM tile serialise on its latency (~200 cycles each, measured),
+    // which at 128 x NT x 16 per instruction is far longer than the math; the epilogue adds the four.
+    static constexpr uint32_t TMEM_COLS = NT * 8;
     static constexpr size_t SMEM = (size_t)RAW_STAGES * RAW_BYTES + A_STAGES * A_BYTES + 1024 + 512;
 };
 
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+        "l"((uint64_t)m), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+// Requests to the copy engine, not bytes, bound this kernel when every k-tile is fetched by its own
+// copies (three requests per 4.6 KB); a stage therefore carries KS k-tiles with three requests in
+// all: one bulk copy of KS packed tiles (contiguous in the tile-major layout), one of their scales,
+// and one 3-D tensor copy that lands the KS X tiles as KS separate swizzled [NT][64] tiles.
 template <int NT>
 __global__ void __launch_bounds__(kFusedThreads, 1)
 fused_small_fwd_kernel(const __grid_constant__ CUtensorMap tmX, FusedParams p) {
@@ -60,8 +74,8 @@ fused_small_fwd_kernel(const __grid_constant__ CUtensorMap tmX, FusedParams p) {
     constexpr int RS = C::RAW_STAGES;
     extern __shared__ uint8_t smem_raw_[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw_ + 1023) & ~(uintptr_t)1023);
-    uint8_t* raw = smem;                                   // RS x RAW_BYTES (each 1024-aligned)
-    uint8_t* abuf = smem + (size_t)RS * C::RAW_BYTES;      // A_STAGES x 16 KB
+    uint8_t* raw = smem;                               // RS x RAW_BYTES (each 1024-aligned)
+    uint8_t* abuf = smem + (size_t)RS * C::RAW_BYTES;  // A_STAGES x 16 KB
     uint64_t* bars = (uint64_t*)(abuf + A_STAGES * A_BYTES);
     uint64_t* full_raw = bars;
     uint64_t* empty_raw = bars + RS;
@@ -79,7 +93,7 @@ fused_small_fwd_kernel(const __grid_constant__ CUtensorMap tmX, FusedParams p) {
             mbar_init(smem_u32(&empty_raw[s]), 1);
         }
         for (int a = 0; a < A_STAGES; ++a) {
-            mbar_init(smem_u32(&full_a[a]), 256);
+            mbar_init(smem_u32(&full_a[a]), 8);  // one arrival per dequant warp of the group that owns the tile
             mbar_init(smem_u32(&empty_a[a]), 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -100,7 +114,8 @@ fused_small_fwd_kernel(const __grid_constant__ CUtensorMap tmX, FusedParams p) {
     const uint32_t tmem_base = *tmem_slot;
 
     const int num_items = p.m_tiles * p.splits;
-    const int groups_per_tile = 64 / p.group;  // 1 (G = 64) or 2 (G = 32)
+    const int gpt = 64 / p.group;  // scale groups per k-tile: 1 (G = 64) or 2 (G = 32)
+    constexpr uint32_t X_OFF = 0, P_OFF = KS * C::X_BYTES, S_OFF = P_OFF + KS * 4096;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -112,17 +127,16 @@ fused_small_fwd_kernel(const __grid_constant__ CUtensorMap tmX, FusedParams p) {
                 const int mt = item / p.splits, z = item - mt * p.splits;
                 const int kt0 = (int)(((long long)z * p.k_tiles) / p.splits);
                 const int kt1 = (int)(((long long)(z + 1) * p.k_tiles) / p.splits);
-                for (int kt = kt0; kt < kt1; ++kt) {
+                for (int kt = kt0; kt < kt1; kt += KS) {
                     if (!mbar_wait(smem_u32(&empty_raw[s]), phase ^ 1u, abort_flag, p.status, 21)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&full_raw[s]);
-                    const int g0 = kt * groups_per_tile;
-                    const int ng = min(groups_per_tile, p.n_groups - g0);  // a trailing half tile has one group
-                    const uint32_t sc_bytes = (uint32_t)ng * 512u;
-                    mbar_expect_tx(bar, C::X_BYTES + 4096u + sc_bytes);
                     const uint32_t base = smem_u32(raw + (size_t)s * C::RAW_BYTES);
-                    tma_load_2d(base, &tmX, bar, kt * 64, 0);
-                    bulk_load(base + C::X_BYTES, p.packed + ((size_t)mt * p.k_tiles + kt) * 4096, 4096u, bar);
-                    bulk_load(base + C::X_BYTES + 4096u, p.scales + ((size_t)mt * p.n_groups + g0) * 128, sc_bytes, bar);
+                    const int tiles = min(KS, kt1 - kt);
+                    const uint32_t pk_bytes = (uint32_t)tiles * 4096u, sc_bytes = (uint32_t)(tiles * gpt) * 512u;
+                    mbar_expect_tx(bar, KS * C::X_BYTES + pk_bytes + sc_bytes);  // the X box is always whole
+                    tma_load_3d(base + X_OFF, &tmX, bar, 0, 0, kt);
+                    bulk_load(base + P_OFF, p.packed + ((size_t)mt * p.k_tiles + kt) * 4096, pk_bytes, bar);
+                    bulk_load(base + S_OFF, p.scales + ((size_t)mt * p.n_groups + (size_t)kt * gpt) * 128, sc_bytes, bar);
                     if (++s == RS) { s = 0; phase ^= 1u; }
                 }
             }
@@ -133,6 +147,8 @@ fused_small_fwd_kernel(const __grid_constant__ CUtensorMap tmX, FusedParams p) {
         if (lane == 0) {
             // ---------------- MMA issuer ----------------
             constexpr uint32_t idesc = make_idesc(1, 1, false, false, 128, NT);
+            const uint32_t d_hi = desc_hi(1024);
+            const uint32_t a_lo0 = desc_lo(smem_u32(abuf), 16), x_lo0 = desc_lo(smem_u32(raw + X_OFF), 16);
             int s = 0, a = 0, acc = 0;
             uint32_t phase = 0, aphase = 0, acc_phase = 0;
             bool ok = true;
@@ -142,22 +158,27 @@ fused_small_fwd_kernel(const __grid_constant__ CUtensorMap tmX, FusedParams p) {
                 const int kt1 = (int)(((long long)(z + 1) * p.k_tiles) / p.splits);
                 if (!mbar_wait(smem_u32(&tempty[acc]), acc_phase ^ 1u, abort_flag, p.status, 22)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * NT);
-                for (int kt = kt0; kt < kt1; ++kt) {
-                    // the dequantised tile (its producers waited for the raw stage, X tile included)
-                    if (!mbar_wait(smem_u32(&full_a[a]), aphase, abort_flag, p.status, 23)) { ok = false; break; }
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * 4 * NT);
+                for (int kt = kt0; ok && kt < kt1; kt += KS) {
                     if (!mbar_wait(smem_u32(&full_raw[s]), phase, abort_flag, p.status, 24)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t sa = smem_u32(abuf + (size_t)a * A_BYTES);
-                    const uint32_t sx = smem_u32(raw + (size_t)s * C::RAW_BYTES);
+                    const int tiles = min(KS, kt1 - kt);
+                    const uint32_t x_lo = x_lo0 + (uint32_t)s * (C::RAW_BYTES >> 4);
+                    for (int j = 0; j < tiles; ++j) {
+                        if (!mbar_wait(smem_u32(&full_a[a]), aphase, abort_flag, p.status, 23)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t a_lo = a_lo0 + (uint32_t)a * (A_BYTES >> 4);
+                        const uint32_t xj_lo = x_lo + (uint32_t)j * (C::X_BYTES >> 4);
+                        const uint32_t accum = (kt > kt0 || j > 0) ? 1u : 0u;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        mma_f16(tmem_d, make_smem_desc(sa + k * 32, 16, 1024), make_smem_desc(sx + k * 32, 16, 1024),
-                                idesc, (kt > kt0 || k > 0) ? 1u : 0u);
-                    mma_commit(smem_u32(&empty_a[a]));
-                    mma_commit(smem_u32(&empty_raw[s]));
+                        for (int k = 0; k < 4; ++k)
+                            mma_f16(tmem_d + (uint32_t)(k * NT), desc_join(a_lo + k * 2u, d_hi), desc_join(xj_lo + k * 2u, d_hi),
+                                    idesc, accum);
+                        mma_commit(smem_u32(&empty_a[a]));
+                        if (++a == A_STAGES) { a = 0; aphase ^= 1u; }
+                    }
+                    if (!ok) break;
+                    mma_commit(smem_u32(&empty_raw[s]));  // the stage (packed tiles, scales, X tiles) is free again
                     if (++s == RS) { s = 0; phase ^= 1u; }
-                    if (++a == A_STAGES) { a = 0; aphase ^= 1u; }
                 }
                 if (!ok) break;
                 mma_commit(smem_u32(&tfull[acc]));
@@ -167,50 +188,54 @@ fused_small_fwd_kernel(const __grid_constant__ CUtensorMap tmX, FusedParams p) {
     } else {
         // ---------------- dequant (warps 2..17: two groups of 256 threads) + epilogue (group 0) --------
         // The groups take alternate k-tiles, so two tiles are converted concurrently; ring positions
-        // are derived from the running tile count, which both groups advance identically.
+        // are derived from running counts that both groups advance identically.
         const int grp = (warp - 2) >> 3;
         const int dt = (threadIdx.x - 64) & 255;
-        const int r = dt >> 1, half = dt & 1;  // row of the tile, 32-k half of it
-        const int quarter = warp & 3;          // TMEM lane quarter of this warp
-        const int chalf = ((warp - 2) >> 2) & 1;  // which half of the NT columns this warp drains
+        const int r = dt >> 1, half = dt & 1;      // row of the tile, 32-k half of it
+        const int quarter = warp & 3;              // TMEM lane quarter of this warp
+        const int chalf = ((warp - 2) >> 2) & 1;   // which half of the NT columns this warp drains
         int acc = 0;
-        uint32_t acc_phase = 0, tix = 0;
+        uint32_t acc_phase = 0, tix = 0, six = 0;  // running k-tile / stage counts
         bool ok = true;
+        const __nv_bfloat162 off = __float2bfloat162_rn(136.f);
         for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
             const int mt = item / p.splits, z = item - mt * p.splits;
             const int kt0 = (int)(((long long)z * p.k_tiles) / p.splits);
             const int kt1 = (int)(((long long)(z + 1) * p.k_tiles) / p.splits);
-            for (int kt = kt0; kt < kt1; ++kt, ++tix) {
-                if ((int)(tix & 1u) != grp) continue;
-                const int s = (int)(tix % RS), a = (int)(tix % A_STAGES);
-                const uint32_t phase = (tix / RS) & 1u, aphase = (tix / A_STAGES) & 1u;
-                if (!mbar_wait(smem_u32(&full_raw[s]), phase, abort_flag, p.status, 25)) { ok = false; break; }
-                if (!mbar_wait(smem_u32(&empty_a[a]), aphase ^ 1u, abort_flag, p.status, 26)) { ok = false; break; }
-                const uint8_t* st = raw + (size_t)s * C::RAW_BYTES + C::X_BYTES;
-                const uint4 v = *((const uint4*)st + dt);  // words 4dt..4dt+3: row r, chunks half*4..+3
-                const int g0 = kt * groups_per_tile;
-                const int gi = groups_per_tile == 2 ? half : 0;
-                float sc = 0.f;
-                if (g0 + gi < p.n_groups) sc = *((const float*)(st + 4096) + gi * 128 + r);
-                const __nv_bfloat162 s2 = __float2bfloat162_rn(sc);
-                const __nv_bfloat162 off = __float2bfloat162_rn(136.f);
-                const uint32_t words[4] = {v.x, v.y, v.z, v.w};
-                uint8_t* arow = abuf + (size_t)a * A_BYTES + r * 128;
+            for (int kt = kt0; ok && kt < kt1; kt += KS, ++six) {
+                const int s = (int)(six % RS);
+                if (!mbar_wait(smem_u32(&full_raw[s]), (six / RS) & 1u, abort_flag, p.status, 25)) { ok = false; break; }
+                const int tiles = min(KS, kt1 - kt);
+                const uint8_t* stage = raw + (size_t)s * C::RAW_BYTES;
+                for (int j = 0; j < tiles; ++j, ++tix) {
+                    if ((int)(tix & 1u) != grp) continue;
+                    const int a = (int)(tix % A_STAGES);
+                    if (!mbar_wait(smem_u32(&empty_a[a]), ((tix / A_STAGES) & 1u) ^ 1u, abort_flag, p.status, 26)) { ok = false; break; }
+                    const uint4 v = *((const uint4*)(stage + P_OFF + j * 4096) + dt);  // row r, chunks half*4..+3
+                    const int gi = gpt == 2 ? half : 0;
+                    const float sc = *((const float*)(stage + S_OFF) + (j * gpt + gi) * 128 + r);
+                    const __nv_bfloat162 s2 = __float2bfloat162_rn(sc);
+                    const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+                    uint8_t* arow = abuf + (size_t)a * A_BYTES + r * 128;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    uint32_t o[4];
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t o[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint32_t t = ((words[i] >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // (128+u_lo, 128+u_hi)
-                        __nv_bfloat162 q = __hsub2(*(__nv_bfloat162*)&t, off);            // exact integers -7..7
-                        __nv_bfloat162 wv = __hmul2(q, s2);
-                        o[j] = *(uint32_t*)&wv;
+                        for (int jj = 0; jj < 4; ++jj) {
+                            uint32_t t = ((words[i] >> (4 * jj)) & 0x000F000Fu) | 0x43004300u;  // (128+u_lo, 128+u_hi)
+                            __nv_bfloat162 q = __hsub2(*(__nv_bfloat162*)&t, off);             // exact integers -7..7
+                            __nv_bfloat162 wv = __hmul2(q, s2);
+                            o[jj] = *(uint32_t*)&wv;
+                        }
+                        const int chunk = (half * 4 + i) ^ (r & 7);  // 128-byte swizzle of the operand layout
+                        *(uint4*)(arow + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
                     }
-                    const int chunk = (half * 4 + i) ^ (r & 7);  // 128-byte swizzle of the operand layout
-                    *(uint4*)(arow + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+                    // every lane publishes its stores to the async proxy; the warp then arrives once
+                    // (256 per-thread arrivals on one barrier serialise and cost more than the tile)
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&full_a[a]));
                 }
-                fence_proxy_async_smem();
-                mbar_arrive(smem_u32(&full_a[a]));
             }
             if (!ok) break;
             if (grp != 0) continue;
@@ -221,15 +246,21 @@ fused_small_fwd_kernel(const __grid_constant__ CUtensorMap tmX, FusedParams p) {
             float* pz = p.part + (size_t)z * p.N * p.M;
 #pragma unroll 1
             for (int c = 0; c < NT / 2; c += 8) {
-                uint32_t rr[8];
+                uint32_t r0[8], r1[8], r2[8], r3[8];
                 const int col0 = chalf * (NT / 2) + c;
-                tmem_ld_x8(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * NT + col0), rr);
+                const uint32_t ta = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * 4 * NT + col0);
+                tmem_ld_x8(ta, r0);
+                tmem_ld_x8(ta + NT, r1);
+                tmem_ld_x8(ta + 2 * NT, r2);
+                tmem_ld_x8(ta + 3 * NT, r3);
                 tmem_ld_wait();
                 if (m < p.M) {
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
                         const int n = col0 + e;
-                        if (n < p.N) pz[(size_t)n * p.M + m] = __uint_as_float(rr[e]);
+                        const float v = (__uint_as_float(r0[e]) + __uint_as_float(r1[e])) +
+                                        (__uint_as_float(r2[e]) + __uint_as_float(r3[e]));
+                        if (n < p.N) pz[(size_t)n * p.M + m] = v;
                     }
                 }
             }
@@ -328,6 +359,36 @@ int pick_splits(int m_tiles, int k_tiles, int sms) {
 
 inline size_t al256(size_t x) { return (x + 255) & ~size_t(255); }
 
+// X [N, K] bf16 viewed as [k-tile][token][64]: dim0 = 64 k of one tile (contiguous), dim1 = tokens
+// (stride K), dim2 = k-tiles (stride 64 elements).  A box {64, NT, KS} then lands KS k-tiles as KS
+// separate 128-byte-swizzled [NT][64] tiles.  Needs K % 64 == 0.
+CUtensorMap make_x_map3d(const void* X, int64_t N, int64_t K, int nt) {
+    typedef CUresult (*Fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                           const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                           CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static Fn fn = nullptr;
+    if (!fn) {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            throw LqError(LQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        fn = (Fn)f;
+    }
+    if (((uintptr_t)X & 15) != 0) throw LqError(LQ_ERR_INVALID, "X must be 16-byte aligned");
+    CUtensorMap m;
+    cuuint64_t dims[3] = {64, (cuuint64_t)N, (cuuint64_t)(K / 64)};
+    cuuint64_t strides[2] = {(cuuint64_t)K * 2, 128};
+    cuuint32_t box[3] = {64, (cuuint32_t)nt, (cuuint32_t)KS};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult rc = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(X), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS)
+        throw LqError(LQ_ERR_CUDA, "cuTensorMapEncodeTiled (3-D X view) failed with CUresult " + std::to_string((int)rc));
+    return m;
+}
+
 template <int NT>
 void launch_fused(const CUtensorMap& tmX, const FusedParams& p, int grid, cudaStream_t st) {
     auto kern = fused_small_fwd_kernel<NT>;
@@ -340,7 +401,7 @@ void launch_fused(const CUtensorMap& tmX, const FusedParams& p, int grid, cudaSt
 }  // namespace
 
 bool lq_fused_supported(const lq_weight* w, int64_t n_tokens, int rank) {
-    return w->scheme == LQ_INT4 && n_tokens >= 1 && n_tokens <= 64 && w->K % 8 == 0 && w->M % 8 == 0 && rank <= 64;
+    return w->scheme == LQ_INT4 && n_tokens >= 1 && n_tokens <= 64 && w->K % 64 == 0 && w->M % 8 == 0 && rank <= 64;
 }
 
 size_t lq_fused_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank) {
@@ -381,7 +442,7 @@ void lq_fused_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, 
     p.status = lq_tc_status_word(w->device);
     const int grid = std::min(p.m_tiles * p.splits, sms);
     const int nt = N <= 16 ? 16 : (N <= 32 ? 32 : 64);
-    CUtensorMap tmX = lq_tc_make_map(X, K, N, K, nt);
+    CUtensorMap tmX = make_x_map3d(X, N, K, nt);
     if (nt == 16) launch_fused<16>(tmX, p, grid, st);
     else if (nt == 32) launch_fused<32>(tmX, p, grid, st);
     else launch_fused<64>(tmX, p, grid, st);

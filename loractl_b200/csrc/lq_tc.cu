@@ -174,6 +174,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
         if (lane == 0) {
             // ---------------- MMA issuer ----------------
             constexpr uint32_t idesc = make_idesc(1, 1, A_MN, B_MN, BM, BLOCK_N);
+            const uint32_t d_hi = desc_hi(1024);
+            const uint32_t a_lo0 = desc_lo(smem_u32(smem_a), A_MN ? 8192 : 16);
+            const uint32_t b_lo0 = desc_lo(smem_u32(smem_b), B_MN ? 8192 : 16);
             int s = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
@@ -188,17 +191,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait(smem_u32(&full[s]), phase, abort_flag, p.status, 13)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem_a + (size_t)s * C::A_BYTES);
-                    const uint32_t sb = smem_u32(smem_b + (size_t)s * C::B_BYTES);
+                    // descriptors: constant high word, low word = stage base + 16-element k-step
+                    // (K-major: 32 bytes along the row; MN-major: 16 k-rows of 128 bytes), in 16-byte units
+                    const uint32_t a_lo = a_lo0 + (uint32_t)s * (C::A_BYTES >> 4);
+                    const uint32_t b_lo = b_lo0 + (uint32_t)s * (C::B_BYTES >> 4);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k) {
-                        // K-major: 16 elements = 32 bytes along the row.  MN-major: 16 k-rows of 128 bytes.
-                        const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024)
-                                                 : make_smem_desc(sa + k * 32, 16, 1024);
-                        const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024)
-                                                 : make_smem_desc(sb + k * 32, 16, 1024);
-                        mma_f16(tmem_d, da, db, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
-                    }
+                    for (int k = 0; k < BK / 16; ++k)
+                        mma_f16(tmem_d, desc_join(a_lo + k * (A_MN ? 128u : 2u), d_hi),
+                                desc_join(b_lo + k * (B_MN ? 128u : 2u), d_hi), idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
                     mma_commit(smem_u32(&empty[s]));  // frees the smem stage once these MMAs retire
                     if (++s == STAGES) { s = 0; phase ^= 1u; }
                 }

@@ -174,6 +174,17 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
     return d;
 }
 
+// The same descriptor split into its 32-bit halves, so that an issue loop adds a pre-shifted byte
+// offset to the low word instead of rebuilding 64 bits per MMA (the MMA-issuing thread is a single
+// lane: every instruction it spends here delays the tensor pipe).
+__device__ __forceinline__ uint32_t desc_hi(uint32_t sbo_bytes) {
+    return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+    return ((saddr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint64_t desc_join(uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; }
+
 // Instruction descriptor (kind::f16 / kind::f8f6f4), dense, f32 accumulator:
 //   [4,6) D format (1 = f32)  [7,10) A format  [10,13) B format  [15] A MN-major  [16] B MN-major
 //   [17,23) N >> 3            [24,29) M >> 4

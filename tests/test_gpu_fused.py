@@ -42,7 +42,8 @@ def test_fused_small_batch_forward_matches_oracle(n, k, m, block, r):
     if n * m >= 1024:
         assert O.cosine(host(y), oy) >= 0.9999
     if r:
-        assert reldev(host(h), oh) <= 2e-5  # H is computed in f32 on this path
+        # the fused path (d_in % 64 == 0) computes H in f32; otherwise H comes from the bf16 GEMM path
+        assert reldev(host(h), oh) <= (2e-5 if k % 64 == 0 else 6e-3)
 
 
 def test_fused_full_size_site_and_determinism():
