@@ -89,12 +89,23 @@ def cpu_reference_rate(workload: str, sample_tokens: int, reps: int, seed: int =
         dx, da, db = O.lora_linear_bwd(dy, x, dequant(), a, b, s)  # ... and again in the backward
         return float(y[0, 0]) + float(dx[0, 0]) + float(da[0, 0]) + float(db[0, 0])
 
-    one_step()
-    t0 = time.perf_counter()
-    for _ in range(reps):
-        one_step()
-    dt = (time.perf_counter() - t0) / reps
+    # torchrun exports OMP_NUM_THREADS=1; the baseline is defined on all host cores, so size the
+    # BLAS pool explicitly and report the thread count actually used
     cores = len(os.sched_getaffinity(0))
+    try:
+        from threadpoolctl import threadpool_limits
+        limiter = threadpool_limits(limits=cores)
+    except Exception:
+        limiter = None
+    try:
+        one_step()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            one_step()
+        dt = (time.perf_counter() - t0) / reps
+    finally:
+        if limiter is not None:
+            limiter.restore_original_limits()
     return step_flops(n, k, m, r) / dt / 1e12, dt, cores
 
 
@@ -213,9 +224,15 @@ def run_ours(args):
     dx_host = torch.empty((n, k), dtype=torch.bfloat16).pin_memory()
     g_host = torch.empty_like(bucket, device="cpu").pin_memory()
 
+    fp8c = args.compute == "fp8"
+    if fp8c:
+        if scheme != "fp8":
+            raise SystemExit("--compute fp8 needs a scaled-fp8 workload (cfg2)")
+        wq.prepare_fp8_backward()
+
     def step(xd, dyd):
-        y, h = Q.linear_fwd_raw(wq, xd, a, b, s)
-        dx, _, _ = Q.linear_bwd_raw(wq, dyd, xd, h, a, b, s, da_out=da, db_out=db)
+        y, h = Q.linear_fwd_raw(wq, xd, a, b, s, fp8_compute=fp8c)
+        dx, _, _ = Q.linear_bwd_raw(wq, dyd, xd, h, a, b, s, da_out=da, db_out=db, fp8_compute=fp8c)
         if world > 1:
             dist.all_reduce(bucket)  # the only exchange of the data-parallel path
         return y, dx
@@ -261,6 +278,14 @@ def run_ours(args):
     lb.check_device_status(dev)
     kinds = {lib.lq_profile_kind_name(i).decode(): (ms_kind[i], int(cnt_kind[i])) for i in range(nk)}
 
+    # The reference's dead-graph guards (crates/loractl-bench/src/lib.rs:35-104): twice the steps must
+    # take about twice as long (ratio in [1.7, 2.3]) and the outputs must be finite and non-zero.
+    ms_2x = timed(lambda: step(x, dy), 2 * args.steps)
+    y_chk, dx_chk = step(x, dy)
+    plausible = bool(torch.isfinite(y_chk).all() and torch.isfinite(dx_chk).all() and torch.isfinite(bucket).all()
+                     and float(y_chk.float().abs().max()) > 0 and float(bucket.abs().max()) > 0)
+    sanity = {"x2_ratio": ms_2x / total_ms, "ok": 1.7 <= ms_2x / total_ms <= 2.3, "plausible": plausible}
+
     # ---- e2e: host buffers in, results out, through the same public calls ----
     # Every step copies its inputs from pinned host memory and its results (Y, dX, dA, dB) back.
     # Copies run on their own streams, double-buffered, so step i's compute overlaps step i+1's
@@ -286,9 +311,9 @@ def run_ours(args):
         s_cmp.wait_event(ev_up[i])
         s_cmp.wait_event(ev_down[i])  # this slot's gradient bucket has been downloaded
         bk = buckets[i]
-        y, h = Q.linear_fwd_raw(wq, xbuf[i], a, b, s)
+        y, h = Q.linear_fwd_raw(wq, xbuf[i], a, b, s, fp8_compute=fp8c)
         dx, _, _ = Q.linear_bwd_raw(wq, dybuf[i], xbuf[i], h, a, b, s, da_out=bk[: k * r].view(k, r),
-                                    db_out=bk[k * r:].view(r, m))
+                                    db_out=bk[k * r:].view(r, m), fp8_compute=fp8c)
         if world > 1:
             dist.all_reduce(bk)
         ev_cmp[i].record(s_cmp)
@@ -333,12 +358,29 @@ def run_ours(args):
             peak_src = f"measured ({peak_kind} cuBLAS bf16, MEASURED_PEAKS.json)"
         else:
             peak, peak_src = 1590.0, "fallback (earlier measurement on this pool)"
+        if fp8c:
+            # No fp8 peak is in MEASURED_PEAKS.json: measure it here the way the bf16 one was measured
+            # (library GEMM, 8192^3, best of 10, CUDA events) and use it as the denominator.
+            a8 = torch.randn(8192, 8192, device=dev).to(torch.float8_e4m3fn)
+            b8 = torch.randn(8192, 8192, device=dev).to(torch.float8_e4m3fn).t()
+            one = torch.ones((), device=dev)
+            best = 1e9
+            for _ in range(13):
+                q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                q0.record()
+                torch._scaled_mm(a8, b8, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+                q1.record()
+                torch.cuda.synchronize()
+                best = min(best, q0.elapsed_time(q1))
+            peak = 2 * 8192 ** 3 / (best * 1e-3) / 1e12
+            peak_src = "measured in this run (burst, torch._scaled_mm e4m3 8192^3, best of 13)"
+            del a8, b8
         gm_ms, gm_n = kinds.get("gemm_main", (0.0, 0))
         achieved = (main_gemm_flops(n, k, m, r) / 2) / (gm_ms / max(gm_n, 1) * 1e-3) / 1e12 if gm_n else None
         roofline = {
             "bound": "tensor", "kernel": "umma_gemm_kernel (frozen GEMM + fused LoRA K extension)",
             "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": (achieved / peak) if achieved else None,
-            "peak_source": peak_src, "traffic": NCU_TRAFFIC_BYTES.get(wl),
+            "peak_source": peak_src, "traffic": None if fp8c else NCU_TRAFFIC_BYTES.get(wl),
             "traffic_unit": "bytes per launch (ncu, full-size launch)",
             "algorithmic_bytes_per_launch": 2 * n * k + 2 * m * k + 2 * n * m,
             "launches_timed": gm_n, "avg_launch_ms": gm_ms / max(gm_n, 1),
@@ -349,7 +391,8 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "vs_baseline": None, "dtype": "fp8 e4m3 x e4m3, f32 accumulate (bf16 in/out)" if fp8c else "bf16",
+            "data": "synthetic",
             "config": {"workload": wl, "scheme": scheme, "d_in": k, "d_out": m, "rank": r, "alpha": alpha,
                        "tokens_per_gpu": n, "parallelism": f"dp{world}",
                        "l2": "inputs larger than L2 (X+dY+Y+dX = 503 MB per step vs 126 MB)"},
@@ -359,6 +402,9 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps},
             "gpu_launches": int(launches),
+            "sanity": sanity,
+            "model": {"step_flops": flops, "main_gemm_flops": main_gemm_flops(n, k, m, r),
+                      "packed_stream_bytes": (k * m + 4 * m) if scheme == "fp8" else (k * m // 2 + 4 * k * m // group)},
             "clocks": clocks,
         }
         print(json.dumps(line))
@@ -482,6 +528,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--compute", default="bf16", choices=["bf16", "fp8"],
+                    help="bf16: weights dequantised to bf16, bf16 MMA (parity-grade); fp8: native e4m3 MMA "
+                         "on the stored fp8 weight with per-token e4m3 activations (scaled-fp8 workloads only)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

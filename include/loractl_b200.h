@@ -43,7 +43,16 @@ typedef enum lq_status {
  * end to end (the reference's own precision on the quant path,
  * crates/loractl-core/src/diffusion_trainer.rs:395-401); LQ_BF16 runs bf16
  * operands with f32 accumulation on the tcgen05 tensor cores. */
-typedef enum lq_dtype { LQ_F32 = 0, LQ_BF16 = 1 } lq_dtype;
+typedef enum lq_dtype {
+    LQ_F32 = 0,
+    LQ_BF16 = 1,
+    /* bf16 activations in and out, but the frozen GEMM runs natively in fp8: the stored e4m3
+     * weight bytes are the MMA operand (no dequantisation pass), activations are quantised to e4m3
+     * with one f32 scale per token, scales are applied in the epilogue (tcgen05 kind::f8f6f4, f32
+     * accumulation).  Scaled-fp8 weights only.  The reference has no fp8 compute at all
+     * (crates/loractl-core/src/fp8.rs decodes at load time); tolerance is correspondingly looser. */
+    LQ_BF16_W8A8 = 2
+} lq_dtype;
 
 /* Storage scheme of a frozen weight.  INT8/INT4 are crates/loractl-core/src/
  * config.rs:637-649 `Quant::{Int8,Int4}` (symmetric, per-block f32 scale);
@@ -167,6 +176,12 @@ int lq_linear_bwd(const lq_weight_t* w, const void* dY, const void* X, const flo
                   int64_t n_tokens, int dtype, const float* A, const float* B, int rank,
                   float scaling, void* dX, float* dA, float* dB, int accumulate,
                   void* workspace, size_t workspace_bytes, void* stream);
+
+/* Builds, once, the transposed copy of a scaled-fp8 weight that the LQ_BF16_W8A8 backward reads
+ * ([d_in, d_out] e4m3 bytes, +1 byte per element of resident memory).  Optional: the first
+ * LQ_BF16_W8A8 backward builds it on demand (one cudaMalloc); call this at load time to keep the
+ * step loop allocation-free.  No counterpart in the reference. */
+int lq_weight_prepare_fp8_backward(const lq_weight_t* w, void* stream);
 
 /* ---- step glue on the flat LoRA buffers ---------------------------------------- */
 

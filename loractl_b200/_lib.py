@@ -13,7 +13,7 @@ import pathlib
 LIB_PATH = pathlib.Path(__file__).resolve().parent / "lib" / "libloractl_b200.so"
 
 LQ_OK, LQ_ERR_INVALID, LQ_ERR_CUDA, LQ_ERR_UNSUPPORTED, LQ_ERR_TIMEOUT, LQ_ERR_WORKSPACE = range(6)
-LQ_F32, LQ_BF16 = 0, 1
+LQ_F32, LQ_BF16, LQ_BF16_W8A8 = 0, 1, 2
 LQ_INT4, LQ_INT8, LQ_FP8_E4M3 = 4, 8, 108
 LQ_SCALE_SCALAR, LQ_SCALE_PER_CHANNEL = 0, 1
 
@@ -52,6 +52,7 @@ SIGNATURES = {
     "lq_linear_workspace_bytes": (_SZ, [_P, _I64, _I, _I]),
     "lq_linear_fwd": (_I, [_P, _P, _I64, _I, _P, _P, _I, _F, _P, _P, _P, _SZ, _P]),
     "lq_linear_bwd": (_I, [_P, _P, _P, _P, _I64, _I, _P, _P, _I, _F, _P, _P, _P, _I, _P, _SZ, _P]),
+    "lq_weight_prepare_fp8_backward": (_I, [_P, _P]),
     "lq_grad_nonfinite_flag": (_I, [_P, _I64, _P, _P]),
     "lq_adamw_step": (_I, [_P, _P, _P, _P, _I64, _F, _F, _F, _F, _F, _I64, _F, _P, _P]),
     "lq_check_device_status": (_I, [_P]),

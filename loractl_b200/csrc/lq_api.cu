@@ -94,6 +94,7 @@ void free_handle(lq_weight* h) {
     cudaFree(h->packed);
     cudaFree(h->scales);
     cudaFree(h->bias);
+    cudaFree(h->packed_t);
     delete h;
 }
 
@@ -128,7 +129,12 @@ struct Carver {
 void check_call(const lq_weight* w, int64_t N, int dtype, const float* A, const float* B, int rank) {
     LQ_CHECK_ARG(w != nullptr, "weight handle is NULL (quant_matmul_t requires a quantized weight)");
     LQ_CHECK_ARG(N >= 0, "n_tokens must be >= 0");
-    LQ_CHECK_ARG(dtype == LQ_F32 || dtype == LQ_BF16, "dtype must be LQ_F32 or LQ_BF16");
+    LQ_CHECK_ARG(dtype == LQ_F32 || dtype == LQ_BF16 || dtype == LQ_BF16_W8A8,
+                 "dtype must be LQ_F32, LQ_BF16 or LQ_BF16_W8A8");
+    if (dtype == LQ_BF16_W8A8 && !lq_w8a8_supported(w, N, rank))
+        throw LqError(LQ_ERR_UNSUPPORTED,
+                      "LQ_BF16_W8A8 (native fp8 compute) needs a scaled-fp8 weight with d_in % 16 == 0 and "
+                      "d_out % 16 == 0; int4/int8 weights compute in bf16 (no fallback is taken silently)");
     LQ_CHECK_ARG(rank >= 0 && rank <= 256, "LoRA rank must be in [0, 256]");
     if (rank > 0) LQ_CHECK_ARG(A != nullptr && B != nullptr, "rank > 0 needs LoRA factors A [K,r] and B [r,M]");
 }
@@ -361,6 +367,8 @@ int lq_dequantize(const lq_weight_t* w, void* out, int out_dtype, void* stream) 
 size_t lq_linear_workspace_bytes(const lq_weight_t* w, int64_t n_tokens, int rank, int dtype) {
     if (!w || n_tokens < 0 || rank < 0) return 0;
     Carver c(nullptr, 0);
+    if (dtype == LQ_BF16_W8A8)
+        return lq_w8a8_supported(w, n_tokens, rank) ? align256(lq_w8a8_workspace_bytes(w, n_tokens, rank)) + 256 : 0;
     if (dtype == LQ_BF16 && lq_tc_supported(w, n_tokens, rank)) {
         size_t need = lq_tc_workspace_bytes(w, n_tokens, rank);  // backward (and forward for N > 64)
         if (lq_fused_supported(w, n_tokens, rank)) need = std::max(need, lq_fused_workspace_bytes(w, n_tokens, rank));
@@ -380,6 +388,10 @@ int lq_linear_fwd(const lq_weight_t* w, const void* X, int64_t n_tokens, int dty
         if (n_tokens == 0) return;
         DeviceGuard dg(w->device);
         cudaStream_t st = (cudaStream_t)stream;
+        if (dtype == LQ_BF16_W8A8) {
+            lq_w8a8_fwd(w, X, n_tokens, A, B, rank, scaling, Y, H_out, workspace, workspace_bytes, st);
+            return;
+        }
         if (dtype == LQ_BF16 && lq_fused_supported(w, n_tokens, rank)) {
             // packed-weight-stream regime: dequantise in shared memory, no bf16 weight in HBM
             lq_fused_fwd(w, X, n_tokens, A, B, rank, scaling, Y, H_out, workspace, workspace_bytes, st);
@@ -415,6 +427,11 @@ int lq_linear_bwd(const lq_weight_t* w, const void* dY, const void* X, const flo
         LQ_CHECK_ARG(rank == 0 || X != nullptr, "X is needed for the LoRA gradients");
         DeviceGuard dg(w->device);
         cudaStream_t st = (cudaStream_t)stream;
+        if (dtype == LQ_BF16_W8A8) {
+            lq_w8a8_bwd(w, dY, X, H, n_tokens, A, B, rank, scaling, dX, dA, dB, accumulate, workspace, workspace_bytes,
+                        st);
+            return;
+        }
         if (dtype == LQ_BF16 && lq_tc_supported(w, n_tokens, rank)) {
             lq_tc_bwd(w, dY, X, H, n_tokens, A, B, rank, scaling, dX, dA, dB, accumulate, workspace, workspace_bytes,
                       st);
@@ -436,6 +453,15 @@ int lq_linear_bwd(const lq_weight_t* w, const void* dY, const void* X, const flo
             Huse = Hbuf;
         }
         bwd_simt(w, dY, X, Huse, n_tokens, dtype, A, B, rank, scaling, dX, dA, dB, accumulate, dH, st);
+    });
+}
+
+int lq_weight_prepare_fp8_backward(const lq_weight_t* w, void* stream) {
+    return guarded([&] {
+        LQ_CHECK_ARG(w != nullptr, "weight handle is NULL");
+        LQ_CHECK_ARG(w->scheme == LQ_FP8_E4M3, "only scaled-fp8 weights have an fp8 backward operand");
+        DeviceGuard dg(w->device);
+        lq_w8a8_prepare_backward(w, (cudaStream_t)stream);
     });
 }
 

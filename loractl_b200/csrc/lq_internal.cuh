@@ -37,6 +37,7 @@ struct lq_weight {
     float* scales = nullptr;
     float* bias = nullptr;
     size_t packed_bytes = 0, scale_bytes = 0;
+    void* packed_t = nullptr;  // fp8 only: the bytes transposed to [d_in, d_out], built on first use
 };
 
 // Device-side view passed to kernels by value.

@@ -18,6 +18,8 @@
 #include <mutex>
 #include <vector>
 
+#include <cuda_fp8.h>
+
 #include "lq_prof.cuh"
 #include "lq_tc.cuh"
 #include "lq_umma.cuh"
@@ -38,6 +40,11 @@ struct GemmParams {
     long long ldc, split_stride;
     const float* bias;
     int* status;
+    // optional epilogue scales: v = acc * row_scale[row] * col_scale[col] (NULL = 1); with
+    // col_scale_bcast the single value col_scale[0] applies to every column
+    const float* row_scale;
+    const float* col_scale;
+    int col_scale_bcast;
 };
 
 template <int BLOCK_N>
@@ -80,12 +87,17 @@ __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* dst, const 
     *(uint4*)dst = u;
 }
 
-template <int BLOCK_N, bool A_MN, bool B_MN, typename OutT>
+// F8: the operands of the first tensor-map pair are e4m3 bytes (128 per k-block row) multiplied
+// with tcgen05.mma kind::f8f6f4; the K-extension pair stays bf16 (kind::f16) and accumulates into
+// the same f32 TMEM tile.  Both pairs must be K-major in that mode.
+template <int BLOCK_N, bool A_MN, bool B_MN, typename OutT, bool F8 = false>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
                  const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1, GemmParams p) {
     using C = Cfg<BLOCK_N>;
     constexpr int STAGES = C::STAGES;
+    static_assert(!(F8 && (A_MN || B_MN)), "fp8 operands are K-major only");
+    constexpr int BK0 = F8 ? 128 : BK;  // elements per k-block of the first pair (128 bytes per row)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_a = smem;
@@ -146,7 +158,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
                     const bool ext = kb >= p.kb0;
                     const CUtensorMap* ma = ext ? &tmA1 : &tmA0;
                     const CUtensorMap* mb = ext ? &tmB1 : &tmB0;
-                    const int kc = (ext ? kb - p.kb0 : kb) * BK;
+                    const int kc = ext ? (kb - p.kb0) * BK : kb * BK0;
                     const uint32_t sa = smem_u32(smem_a + (size_t)s * C::A_BYTES);
                     const uint32_t sb = smem_u32(smem_b + (size_t)s * C::B_BYTES);
                     if (!A_MN) {
@@ -174,6 +186,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
         if (lane == 0) {
             // ---------------- MMA issuer ----------------
             constexpr uint32_t idesc = make_idesc(1, 1, A_MN, B_MN, BM, BLOCK_N);
+            constexpr uint32_t idesc8 = make_idesc(0, 0, false, false, BM, BLOCK_N);  // e4m3 x e4m3
             const uint32_t d_hi = desc_hi(1024);
             const uint32_t a_lo0 = desc_lo(smem_u32(smem_a), A_MN ? 8192 : 16);
             const uint32_t b_lo0 = desc_lo(smem_u32(smem_b), B_MN ? 8192 : 16);
@@ -195,10 +208,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
                     // (K-major: 32 bytes along the row; MN-major: 16 k-rows of 128 bytes), in 16-byte units
                     const uint32_t a_lo = a_lo0 + (uint32_t)s * (C::A_BYTES >> 4);
                     const uint32_t b_lo = b_lo0 + (uint32_t)s * (C::B_BYTES >> 4);
+                    if (F8 && kb < p.kb0) {
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        mma_f16(tmem_d, desc_join(a_lo + k * (A_MN ? 128u : 2u), d_hi),
-                                desc_join(b_lo + k * (B_MN ? 128u : 2u), d_hi), idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < 4; ++k)  // 32 e4m3 per instruction = 32 bytes along the row
+                            mma_f8(tmem_d, desc_join(a_lo + k * 2u, d_hi), desc_join(b_lo + k * 2u, d_hi), idesc8,
+                                   (kb > kb_begin || k > 0) ? 1u : 0u);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < BK / 16; ++k)
+                            mma_f16(tmem_d, desc_join(a_lo + k * (A_MN ? 128u : 2u), d_hi),
+                                    desc_join(b_lo + k * (B_MN ? 128u : 2u), d_hi), idesc,
+                                    (kb > kb_begin || k > 0) ? 1u : 0u);
+                    }
                     mma_commit(smem_u32(&empty[s]));  // frees the smem stage once these MMAs retire
                     if (++s == STAGES) { s = 0; phase ^= 1u; }
                 }
@@ -221,6 +242,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
             tc_fence_after();
             const int row = m_tile * BM + quarter * 32 + lane;
             OutT* crow = Cbase + (long long)z * p.split_stride + (long long)row * p.ldc;
+            const float rs = (p.row_scale && row < p.Mg) ? p.row_scale[row] : 1.f;
 #pragma unroll 1
             for (int c = 0; c < BLOCK_N / 32; ++c) {
                 uint32_t r[32];
@@ -235,6 +257,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
                             float v[8];
 #pragma unroll
                             for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+                            if (p.row_scale || p.col_scale) {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e)
+                                    v[e] *= rs * (p.col_scale ? p.col_scale[p.col_scale_bcast ? 0 : col + e] : 1.f);
+                            }
                             if (p.bias) {
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) v[e] += p.bias[col + e];
@@ -260,15 +287,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
 
 // ---- small elementwise helpers ----------------------------------------------------------
 
-// out[i * ldo + j] = bf16(alpha * in[i * si + j * sj]) for j < J, 0 for J <= j < Jpad.
+// out[i * ldo + j] = bf16(alpha * in[i * si + j * sj] / div_i) for j < J, 0 for J <= j < Jpad, where
+// div_i = row_div[i] (or row_div[0] with row_div_bcast), 1 when row_div is NULL.
 __global__ void __launch_bounds__(256) cast_pad_kernel(const float* __restrict__ in, long long si, long long sj,
                                                        __nv_bfloat16* __restrict__ out, long long ldo, long long I,
-                                                       int J, int Jpad, float alpha) {
+                                                       int J, int Jpad, float alpha,
+                                                       const float* __restrict__ row_div, int row_div_bcast) {
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= I * Jpad) return;
     long long i = idx / Jpad;
     int j = (int)(idx - i * Jpad);
     float v = j < J ? alpha * in[i * si + j * sj] : 0.f;
+    if (row_div) v = __fdiv_rn(v, row_div[row_div_bcast ? 0 : i]);
     out[i * ldo + j] = __float2bfloat16(v);
 }
 
@@ -281,7 +311,8 @@ __global__ void __launch_bounds__(256) reduce_partials_kernel(const float* __res
                                                               float alpha, float* __restrict__ out, long long ldo,
                                                               int transposed, int accumulate,
                                                               __nv_bfloat16* __restrict__ ext, long long ld_ext,
-                                                              float ext_scale) {
+                                                              float ext_scale,
+                                                              const float* __restrict__ ext_row_div = nullptr) {
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= I * Jpad) return;
     long long i = idx / Jpad;
@@ -295,7 +326,11 @@ __global__ void __launch_bounds__(256) reduce_partials_kernel(const float* __res
             out[o] = accumulate ? out[o] + v : v;
         }
     }
-    if (ext) ext[i * ld_ext + j] = __float2bfloat16(j < J ? ext_scale * v : 0.f);
+    if (ext) {
+        float e = j < J ? ext_scale * v : 0.f;
+        if (ext_row_div) e = __fdiv_rn(e, ext_row_div[i]);  // pre-divide by the row scale the epilogue multiplies back
+        ext[i * ld_ext + j] = __float2bfloat16(e);
+    }
 }
 
 // ---- host side -------------------------------------------------------------------------
@@ -319,15 +354,19 @@ EncodeTiledFn encode_fn() {
 }
 
 // 2-D bf16 tensor [rows, inner] with `ld` elements between rows; box = 64 x box_rows, 128-byte swizzle.
-CUtensorMap make_map(const void* base, int64_t inner, int64_t rows, int64_t ld, int box_rows) {
+// `u8`: one-byte elements (e4m3 bytes), box 128 x box_rows; otherwise bf16, box 64 x box_rows — 128 bytes per box
+// row either way.
+CUtensorMap make_map(const void* base, int64_t inner, int64_t rows, int64_t ld, int box_rows, bool u8 = false) {
+    const int esz = u8 ? 1 : 2;
     if (((uintptr_t)base & 15) != 0) throw LqError(LQ_ERR_INVALID, "tensor-core path: pointers must be 16-byte aligned");
-    if ((ld * 2) % 16 != 0) throw LqError(LQ_ERR_INVALID, "tensor-core path: row stride must be a multiple of 16 bytes");
+    if ((ld * esz) % 16 != 0) throw LqError(LQ_ERR_INVALID, "tensor-core path: row stride must be a multiple of 16 bytes");
     CUtensorMap m;
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * esz};
+    cuuint32_t box[2] = {u8 ? 128u : 64u, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1u, 1u};
-    CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+    CUresult r = encode_fn()(&m, u8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                             const_cast<void*>(base), dims, strides, box, estr,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
@@ -360,10 +399,16 @@ struct Operand {
     int64_t ld;       // elements between consecutive rows of the stored matrix
 };
 
-template <int BLOCK_N, bool A_MN, bool B_MN, typename OutT>
+struct EpiScales {
+    const float* row = nullptr;  // [Mg]
+    const float* col = nullptr;  // [Ng], or one value when col_bcast
+    int col_bcast = 0;
+};
+
+template <int BLOCK_N, bool A_MN, bool B_MN, typename OutT, bool F8 = false>
 void launch_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand* a1, const Operand* b1, int64_t K1,
                  OutT* Cout, int64_t ldc, int64_t split_stride, int64_t Mg, int64_t Ng, int splits, const float* bias,
-                 cudaStream_t st, int64_t b_rows = -1, int prof_kind = LQ_K_GEMM_MAIN) {
+                 cudaStream_t st, int64_t b_rows = -1, int prof_kind = LQ_K_GEMM_MAIN, EpiScales sc = EpiScales()) {
     // b_rows: rows the B operand really has when fewer than Ng (TMA zero-fills the rest).
     using C = Cfg<BLOCK_N>;
     if (b_rows < 0) b_rows = Ng;
@@ -376,12 +421,14 @@ void launch_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand
     auto mapB = [&](const Operand& o, int64_t Kg) {
         return B_MN ? make_map(o.ptr, b_rows, Kg, o.ld, 64) : make_map(o.ptr, Kg, b_rows, o.ld, BLOCK_N);
     };
-    CUtensorMap tA0 = mapA(a0, K0), tB0 = mapB(b0, K0);
+    CUtensorMap tA0 = F8 ? make_map(a0.ptr, K0, Mg, a0.ld, BM, true) : mapA(a0, K0);
+    CUtensorMap tB0 = F8 ? make_map(b0.ptr, K0, b_rows, b0.ld, BLOCK_N, true) : mapB(b0, K0);
     CUtensorMap tA1 = a1 ? mapA(*a1, K1) : tA0, tB1 = b1 ? mapB(*b1, K1) : tB0;
+    constexpr int BK0 = F8 ? 128 : BK;
     GemmParams p;
     p.Mg = (int)Mg;
     p.Ng = (int)Ng;
-    p.kb0 = (int)((K0 + BK - 1) / BK);
+    p.kb0 = (int)((K0 + BK0 - 1) / BK0);
     p.kb1 = a1 ? (int)((K1 + BK - 1) / BK) : 0;
     p.m_tiles = (int)((Mg + BM - 1) / BM);
     p.n_tiles = (int)((Ng + BLOCK_N - 1) / BLOCK_N);
@@ -391,9 +438,12 @@ void launch_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand
     p.split_stride = split_stride;
     p.bias = bias;
     p.status = ctx.status;
+    p.row_scale = sc.row;
+    p.col_scale = sc.col;
+    p.col_scale_bcast = sc.col_bcast;
     long long items = (long long)p.m_tiles * p.n_tiles * splits;
     int grid = (int)std::min<long long>(items, ctx.sm_count);
-    auto kern = umma_gemm_kernel<BLOCK_N, A_MN, B_MN, OutT>;
+    auto kern = umma_gemm_kernel<BLOCK_N, A_MN, B_MN, OutT, F8>;
     LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
     LqProf prof(prof_kind, st);
     kern<<<grid, kThreads, C::SMEM, st>>>(tA0, tB0, tA1, tB1, p);
@@ -452,7 +502,7 @@ TcWs carve_tc(const lq_weight* w, int64_t N, int r, void* base, int sm_count) {
 // Out[I, r] = alpha * Z[I, C] . P[r, C]^T  via split-K tcgen05 GEMM + fixed-order reduce.
 void skinny_down(const void* Z, int64_t I, int64_t Cdim, int64_t ldz, const __nv_bfloat16* P, int64_t ldp_in, int r,
                  float alpha, float* out_f32, __nv_bfloat16* ext, float ext_scale, float* part, int sm_count,
-                 cudaStream_t st) {
+                 cudaStream_t st, const float* ext_row_div = nullptr) {
     const int EXT = ext_width(r);
     const int64_t kb = (Cdim + BK - 1) / BK;
     const int64_t m_tiles = (I + BM - 1) / BM, n_tiles = EXT / 64;
@@ -464,7 +514,7 @@ void skinny_down(const void* Z, int64_t I, int64_t Cdim, int64_t ldz, const __nv
     LqProf prof(LQ_K_REDUCE, st);
     reduce_partials_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(part, I * (long long)EXT, splits, EXT, I, r,
                                                                           EXT, alpha, out_f32, r, 0, 0, ext, EXT,
-                                                                          ext_scale);
+                                                                          ext_scale, ext_row_div);
     LQ_CUDA(cudaGetLastError());
 }
 
@@ -487,11 +537,12 @@ void skinny_grad(const void* Z, int64_t Nred, int64_t Cdim, int64_t ldz, const _
 }
 
 void cast_pad(const float* in, long long si, long long sj, __nv_bfloat16* out, long long ldo, long long I, int J,
-              int Jpad, float alpha, cudaStream_t st) {
+              int Jpad, float alpha, cudaStream_t st, const float* row_div = nullptr, int row_div_bcast = 0) {
     long long total = I * Jpad;
     if (total <= 0) return;
     LqProf prof(LQ_K_PREP, st);
-    cast_pad_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(in, si, sj, out, ldo, I, J, Jpad, alpha);
+    cast_pad_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(in, si, sj, out, ldo, I, J, Jpad, alpha, row_div,
+                                                                     row_div_bcast);
     LQ_CUDA(cudaGetLastError());
 }
 
@@ -515,6 +566,239 @@ void main_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand* 
     } else {
         launch_gemm<192, false, false, OutT>(a0, b0, K0, a1, b1, K1, Cout, ldc, 0, Mg, Ng, 1, bias, st);
     }
+}
+
+
+// =========================================================================================
+// Native fp8 compute (w8a8): e4m3 weights straight from HBM x e4m3 activations
+// =========================================================================================
+//
+// For scaled-fp8 weights the frozen GEMM can run on tcgen05's kind::f8f6f4 at twice the bf16 rate
+// with NO dequantisation pass: TMA loads the stored e4m3 bytes as the MMA operand.  The activations
+// are quantised to e4m3 on the fly with one f32 scale per token (absmax / 448); the scales are
+// applied in the epilogue, v = acc * s_row[n] * s_w[m].  In the backward the weight scale lies on
+// the reduction axis (dX = (dY . diag(s_w)) . W8), so it is folded into dY before dY is quantised.
+// The LoRA K extension stays bf16 (its operands are pre-divided by the scales the epilogue applies),
+// so the trained low-rank path never passes through 8 bits.
+
+// One block per row: q[n, :] = e4m3(x[n, :] * colmul[:] / s_n), s_n = max(absmax / 448, 1e-12).
+__global__ void __launch_bounds__(256) quant_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ x, long long C,
+                                                              const float* __restrict__ colmul,
+                                                              uint8_t* __restrict__ q, float* __restrict__ scale) {
+    __shared__ float red[8];
+    __shared__ float s_inv;
+    const long long n = blockIdx.x;
+    const __nv_bfloat16* xr = x + n * C;
+    float amax = 0.f;
+    for (long long c = (long long)threadIdx.x * 8; c < C; c += 256 * 8) {  // C % 8 == 0
+        const uint4 v = *(const uint4*)(xr + c);
+        const __nv_bfloat162* h = (const __nv_bfloat162*)&v;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float2 f = __bfloat1622float2(h[e]);
+            if (colmul) { f.x *= colmul[c + 2 * e]; f.y *= colmul[c + 2 * e + 1]; }
+            amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+    }
+    for (int off = 16; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float a = red[0];
+        for (int i = 1; i < 8; ++i) a = fmaxf(a, red[i]);
+        const float s = fmaxf(__fdiv_rn(a, 448.f), 1e-12f);
+        scale[n] = s;
+        s_inv = __fdiv_rn(1.f, s);
+    }
+    __syncthreads();
+    const float inv = s_inv;
+    uint8_t* qr = q + n * C;
+    for (long long c = (long long)threadIdx.x * 8; c < C; c += 256 * 8) {
+        const uint4 v = *(const uint4*)(xr + c);  // second read of the row: L1/L2 hit
+        const __nv_bfloat162* h = (const __nv_bfloat162*)&v;
+        uint32_t out[2] = {0u, 0u};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float2 f = __bfloat1622float2(h[e]);
+            if (colmul) { f.x *= colmul[c + 2 * e]; f.y *= colmul[c + 2 * e + 1]; }
+            f.x *= inv;
+            f.y *= inv;
+            const uint32_t pr = (uint32_t)__nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);  // RNE, saturating
+            out[e >> 1] |= pr << (16 * (e & 1));
+        }
+        *(uint2*)(qr + c) = make_uint2(out[0], out[1]);
+    }
+}
+
+// Same result, single pass over HBM: a persistent block walks rows; every thread owns a fixed set of
+// 8-column vectors (VPT of them), keeps their column multipliers in registers for the whole launch
+// and the row's values in registers between the absmax reduction and the conversion.
+template <int VPT>
+__global__ void __launch_bounds__(256) quant_rows_e4m3_reg_kernel(const __nv_bfloat16* __restrict__ x, long long N,
+                                                                  long long C, const float* __restrict__ colmul,
+                                                                  uint8_t* __restrict__ q, float* __restrict__ scale) {
+    __shared__ float red[2][8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float cm[VPT][8];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const long long c = ((long long)i * 256 + threadIdx.x) * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) cm[i][e] = (colmul && c < C) ? colmul[c + e] : 1.f;
+    }
+    int buf = 0;
+    for (long long n = blockIdx.x; n < N; n += gridDim.x, buf ^= 1) {
+        const __nv_bfloat16* xr = x + n * C;
+        float f[VPT][8];
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const long long c = ((long long)i * 256 + threadIdx.x) * 8;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (c < C) v = *(const uint4*)(xr + c);
+            const __nv_bfloat162* h = (const __nv_bfloat162*)&v;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 t = __bfloat1622float2(h[e]);
+                f[i][2 * e] = t.x * cm[i][2 * e];
+                f[i][2 * e + 1] = t.y * cm[i][2 * e + 1];
+                amax = fmaxf(amax, fmaxf(fabsf(f[i][2 * e]), fabsf(f[i][2 * e + 1])));
+            }
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        if (lane == 0) red[buf][warp] = amax;
+        __syncthreads();  // double-buffered: the next row's writes go to the other half
+        float a = red[buf][0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) a = fmaxf(a, red[buf][i]);
+        const float s = fmaxf(__fdiv_rn(a, 448.f), 1e-12f);
+        const float inv = __fdiv_rn(1.f, s);
+        if (threadIdx.x == 0) scale[n] = s;
+        uint8_t* qr = q + n * C;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const long long c = ((long long)i * 256 + threadIdx.x) * 8;
+            if (c < C) {
+                uint32_t out[2] = {0u, 0u};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 t = make_float2(f[i][2 * e] * inv, f[i][2 * e + 1] * inv);
+                    const uint32_t pr = (uint32_t)__nv_cvt_float2_to_fp8x2(t, __NV_SATFINITE, __NV_E4M3);
+                    out[e >> 1] |= pr << (16 * (e & 1));
+                }
+                *(uint2*)(qr + c) = make_uint2(out[0], out[1]);
+            }
+        }
+    }
+}
+
+// out[k, m] = in[m, k] for e4m3 bytes (load-time: the backward wants the weight K-major in d_out).
+__global__ void __launch_bounds__(256) transpose_u8_kernel(const uint8_t* __restrict__ in, long long M, long long K,
+                                                           uint8_t* __restrict__ out) {
+    __shared__ uint8_t t[64][65];
+    const long long m0 = (long long)blockIdx.y * 64, k0 = (long long)blockIdx.x * 64;
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+    for (int i = ty; i < 64; i += 4)
+        t[i][tx] = (m0 + i < M && k0 + tx < K) ? in[(m0 + i) * K + k0 + tx] : 0;
+    __syncthreads();
+    for (int i = ty; i < 64; i += 4)
+        if (k0 + i < K && m0 + tx < M) out[(k0 + i) * M + m0 + tx] = t[tx][i];
+}
+
+struct W8Ws {
+    uint8_t* q8;          // quantised activations: [N, K] (fwd) or [N, M] (bwd)
+    float* srow;          // [N] per-token scale
+    float* Hf;            // [N, r]
+    float* dHf;           // [N, r]
+    __nv_bfloat16* ext_a; // [N, EXT]  extension operand (pre-divided by the row scale)
+    __nv_bfloat16* ext_b; // [N, EXT]  s*H   (dB operand)
+    __nv_bfloat16* ext_c; // [N, EXT]  dH    (dA operand)
+    __nv_bfloat16* pdown; // A^T [r, K] / B [r, M]
+    __nv_bfloat16* pext;  // B^T [M, EXT] / A [K, EXT]
+    float* part;
+    size_t bytes;
+};
+
+W8Ws carve_w8(const lq_weight* w, int64_t N, int r, void* base) {
+    const size_t M = (size_t)w->M, K = (size_t)w->K;
+    const size_t EXT = (size_t)ext_width(r > 0 ? r : 1);
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        size_t o = al256(off);
+        off = o + bytes;
+        return base ? (void*)((char*)base + o) : nullptr;
+    };
+    W8Ws t{};
+    t.q8 = (uint8_t*)take((size_t)N * std::max(M, K));
+    t.srow = (float*)take((size_t)N * 4);
+    if (r > 0) {
+        t.Hf = (float*)take((size_t)N * r * 4);
+        t.dHf = (float*)take((size_t)N * r * 4);
+        t.ext_a = (__nv_bfloat16*)take((size_t)N * EXT * 2);
+        t.ext_b = (__nv_bfloat16*)take((size_t)N * EXT * 2);
+        t.ext_c = (__nv_bfloat16*)take((size_t)N * EXT * 2);
+        t.pdown = (__nv_bfloat16*)take((size_t)r * std::max(M, K) * 2);
+        t.pext = (__nv_bfloat16*)take(std::max(M, K) * EXT * 2);
+        t.part = (float*)take((size_t)16 * std::max((size_t)N, std::max(M, K)) * EXT * 4);
+    }
+    t.bytes = al256(off);
+    return t;
+}
+
+void quant_rows(const void* x, int64_t N, int64_t C, const float* colmul, uint8_t* q, float* scale, cudaStream_t st) {
+    LqProf prof(LQ_K_DEQUANT, st);
+    const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
+    const unsigned grid = (unsigned)std::min<int64_t>(N, 148 * 4);
+    const int64_t vec = (C + 2047) / 2048;  // 8-column vectors per thread
+    if (vec <= 2) quant_rows_e4m3_reg_kernel<2><<<grid, 256, 0, st>>>(xb, N, C, colmul, q, scale);
+    else if (vec <= 4) quant_rows_e4m3_reg_kernel<4><<<grid, 256, 0, st>>>(xb, N, C, colmul, q, scale);
+    else if (vec <= 6) quant_rows_e4m3_reg_kernel<6><<<grid, 256, 0, st>>>(xb, N, C, colmul, q, scale);
+    else if (vec <= 8) quant_rows_e4m3_reg_kernel<8><<<grid, 256, 0, st>>>(xb, N, C, colmul, q, scale);
+    else quant_rows_e4m3_kernel<<<(unsigned)N, 256, 0, st>>>(xb, C, colmul, q, scale);
+    LQ_CUDA(cudaGetLastError());
+}
+
+void main_gemm_f8(const Operand& a0, const Operand& b0, int64_t K0, const Operand* a1, const Operand* b1, int64_t K1,
+                  __nv_bfloat16* Cout, int64_t ldc, int64_t Mg, int64_t Ng, const float* bias, const EpiScales& sc,
+                  int sm_count, cudaStream_t st) {
+    const int64_t m_tiles = (Mg + BM - 1) / BM;
+    auto waves_eff = [&](int bn) {
+        const int64_t tiles = m_tiles * ((Ng + bn - 1) / bn);
+        const int64_t rounds = (tiles + sm_count - 1) / sm_count;
+        const double pad = (double)Ng / (double)(((Ng + bn - 1) / bn) * bn);
+        return pad * (double)tiles / (double)(rounds * sm_count);
+    };
+    using T = __nv_bfloat16;
+    if (Ng <= 128)
+        launch_gemm<128, false, false, T, true>(a0, b0, K0, a1, b1, K1, Cout, ldc, 0, Mg, Ng, 1, bias, st, -1, LQ_K_GEMM_MAIN, sc);
+    else if (Ng > 192 && waves_eff(256) >= 0.95 * waves_eff(192))
+        launch_gemm<256, false, false, T, true>(a0, b0, K0, a1, b1, K1, Cout, ldc, 0, Mg, Ng, 1, bias, st, -1, LQ_K_GEMM_MAIN, sc);
+    else
+        launch_gemm<192, false, false, T, true>(a0, b0, K0, a1, b1, K1, Cout, ldc, 0, Mg, Ng, 1, bias, st, -1, LQ_K_GEMM_MAIN, sc);
+}
+
+std::mutex g_wt_mu;
+
+// The e4m3 weight transposed to [d_in, d_out], built once per handle (first w8a8 backward, or
+// explicitly at load time) so that the dX contraction is K-major in d_out like every other operand.
+const uint8_t* ensure_transposed(const lq_weight* w, cudaStream_t st) {
+    std::lock_guard<std::mutex> lk(g_wt_mu);
+    lq_weight* mw = const_cast<lq_weight*>(w);
+    if (!mw->packed_t) {
+        void* buf = nullptr;
+        LQ_CUDA(cudaMalloc(&buf, (size_t)w->M * (size_t)w->K));
+        dim3 grid((unsigned)((w->K + 63) / 64), (unsigned)((w->M + 63) / 64));
+        LqProf prof(LQ_K_QUANT, st);
+        transpose_u8_kernel<<<grid, 256, 0, st>>>((const uint8_t*)w->packed, w->M, w->K, (uint8_t*)buf);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) {
+            cudaFree(buf);
+            throw LqError(LQ_ERR_CUDA, std::string("transpose_u8_kernel: ") + cudaGetErrorString(e));
+        }
+        mw->packed_t = buf;
+    }
+    return (const uint8_t*)mw->packed_t;
 }
 
 }  // namespace
@@ -607,6 +891,105 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
             skinny_down(X, N, K, K, t.pdown, K, r, 1.f, t.Hf, t.ext_b, s, t.part, ctx.sm_count, st);
         } else {
             cast_pad(Hsrc, r, 1, t.ext_b, EXT, N, r, EXT, s, st);
+        }
+        skinny_grad(dY, N, M, M, t.ext_b, r, 1.f, dB, 1, accumulate, t.part, ctx.sm_count, st);
+    }
+}
+
+// ---- native fp8 (w8a8) entry points ------------------------------------------------------
+
+bool lq_w8a8_supported(const lq_weight* w, int64_t n_tokens, int rank) {
+    (void)n_tokens;
+    (void)rank;
+    return w->scheme == LQ_FP8_E4M3 && w->K % 16 == 0 && w->M % 16 == 0;
+}
+
+size_t lq_w8a8_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank) {
+    return carve_w8(w, n_tokens, rank, nullptr).bytes;
+}
+
+void lq_w8a8_prepare_backward(const lq_weight* w, cudaStream_t st) { ensure_transposed(w, st); }
+
+void lq_w8a8_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, const float* B, int r, float s, void* Y,
+                 float* H_out, void* ws, size_t ws_bytes, cudaStream_t st) {
+    const int64_t M = w->M, K = w->K;
+    DevCtx& ctx = dev_ctx(w->device);
+    LQ_CHECK_ARG(ws != nullptr && ((uintptr_t)ws & 255) == 0, "workspace must be non-NULL and 256-byte aligned");
+    W8Ws t = carve_w8(w, N, r, ws);
+    if (t.bytes > ws_bytes)
+        throw LqError(LQ_ERR_WORKSPACE, "workspace too small: need " + std::to_string(t.bytes) + " bytes, got " +
+                                            std::to_string(ws_bytes));
+    const bool per_channel = w->scale_kind == LQ_SCALE_PER_CHANNEL;
+    // 1. X -> e4m3 with one scale per token
+    quant_rows(X, N, K, nullptr, t.q8, t.srow, st);
+    EpiScales sc;
+    sc.row = t.srow;
+    sc.col = w->scales;
+    sc.col_bcast = per_channel ? 0 : 1;
+    Operand a0{t.q8, false, K}, b0{w->packed, false, K};
+    if (r == 0) {
+        main_gemm_f8(a0, b0, K, nullptr, nullptr, 0, (__nv_bfloat16*)Y, M, N, M, w->bias, sc, ctx.sm_count, st);
+        return;
+    }
+    const int EXT = ext_width(r);
+    // 2. H = X . A (bf16 operands, f32 out); extension operand s*H / s_x[n]
+    cast_pad(A, 1, r, t.pdown, K, r, (int)K, (int)K, 1.f, st);
+    float* Hf = H_out ? H_out : t.Hf;
+    skinny_down(X, N, K, K, t.pdown, K, r, 1.f, Hf, t.ext_a, s, t.part, ctx.sm_count, st, t.srow);
+    // 3. B^T / s_w[m], then Y = (X8 . W8^T + ext) * s_x[n] * s_w[m] + bias
+    cast_pad(B, 1, M, t.pext, EXT, M, r, EXT, 1.f, st, w->scales, per_channel ? 0 : 1);
+    Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
+    main_gemm_f8(a0, b0, K, &a1, &b1, EXT, (__nv_bfloat16*)Y, M, N, M, w->bias, sc, ctx.sm_count, st);
+}
+
+void lq_w8a8_bwd(const lq_weight* w, const void* dY, const void* X, const float* H, int64_t N, const float* A,
+                 const float* B, int r, float s, void* dX, float* dA, float* dB, int accumulate, void* ws,
+                 size_t ws_bytes, cudaStream_t st) {
+    const int64_t M = w->M, K = w->K;
+    DevCtx& ctx = dev_ctx(w->device);
+    LQ_CHECK_ARG(ws != nullptr && ((uintptr_t)ws & 255) == 0, "workspace must be non-NULL and 256-byte aligned");
+    W8Ws t = carve_w8(w, N, r, ws);
+    if (t.bytes > ws_bytes)
+        throw LqError(LQ_ERR_WORKSPACE, "workspace too small: need " + std::to_string(t.bytes) + " bytes, got " +
+                                            std::to_string(ws_bytes));
+    const bool per_channel = w->scale_kind == LQ_SCALE_PER_CHANNEL;
+    const int EXT = ext_width(r > 0 ? r : 1);
+    const uint8_t* wt = nullptr;
+    EpiScales sc;
+    if (dX) {
+        wt = ensure_transposed(w, st);
+        // dY' = dY * s_w[m] (per-channel scale folded in: it lies on the reduction axis), then e4m3 per token
+        quant_rows(dY, N, M, per_channel ? w->scales : nullptr, t.q8, t.srow, st);
+        sc.row = t.srow;
+        if (!per_channel) { sc.col = w->scales; sc.col_bcast = 1; }
+    }
+    Operand a0{t.q8, false, M}, b0{wt, false, M};
+    if (r == 0) {
+        if (dX) main_gemm_f8(a0, b0, M, nullptr, nullptr, 0, (__nv_bfloat16*)dX, K, N, K, nullptr, sc, ctx.sm_count, st);
+        return;
+    }
+    // dH = s * dY . B^T from the bf16 dY; extension operand dH / s_dy[n] (and / s_w when that is a scalar)
+    cast_pad(B, M, 1, t.pdown, M, r, (int)M, (int)M, 1.f, st);
+    skinny_down(dY, N, M, M, t.pdown, M, r, s, t.dHf, t.ext_a, 1.f, t.part, ctx.sm_count, st, dX ? t.srow : nullptr);
+    if (dX) {
+        cast_pad(A, r, 1, t.pext, EXT, K, r, EXT, 1.f, st, per_channel ? nullptr : w->scales, 1);
+        Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
+        main_gemm_f8(a0, b0, M, &a1, &b1, EXT, (__nv_bfloat16*)dX, K, N, K, nullptr, sc, ctx.sm_count, st);
+    }
+    if (dA) {  // dA = X^T . dH with the plain bf16 dH
+        const __nv_bfloat16* dh_plain = t.ext_a;
+        if (dX) {
+            cast_pad(t.dHf, r, 1, t.ext_c, EXT, N, r, EXT, 1.f, st);
+            dh_plain = t.ext_c;
+        }
+        skinny_grad(X, N, K, K, dh_plain, r, 1.f, dA, 0, accumulate, t.part, ctx.sm_count, st);
+    }
+    if (dB) {
+        if (!H) {
+            cast_pad(A, 1, r, t.pdown, K, r, (int)K, (int)K, 1.f, st);
+            skinny_down(X, N, K, K, t.pdown, K, r, 1.f, t.Hf, t.ext_b, s, t.part, ctx.sm_count, st);
+        } else {
+            cast_pad(H, r, 1, t.ext_b, EXT, N, r, EXT, s, st);
         }
         skinny_grad(dY, N, M, M, t.ext_b, r, 1.f, dB, 1, accumulate, t.part, ctx.sm_count, st);
     }
@@ -727,6 +1110,9 @@ void launch_static_split(const void* A, int64_t lda, const void* B, int64_t ldb,
     p.split_stride = Mg * ldp;
     p.bias = nullptr;
     p.status = ctx.status;
+    p.row_scale = nullptr;
+    p.col_scale = nullptr;
+    p.col_scale_bcast = 0;
     long long items = (long long)p.m_tiles * p.n_tiles * splits;
     int grid = (int)std::min<long long>(items, ctx.sm_count);
     auto kern = umma_gemm_kernel<64, MN, MN, float>;

@@ -37,3 +37,14 @@ bool lq_fused_supported(const lq_weight* w, int64_t n_tokens, int rank);
 size_t lq_fused_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank);
 void lq_fused_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, const float* B, int r, float s,
                   void* Y, float* H_out, void* ws, size_t ws_bytes, cudaStream_t st);
+
+// Native fp8 compute (scaled-fp8 weights only): e4m3 weights straight from HBM x per-token e4m3
+// activations on tcgen05 kind::f8f6f4, scales applied in the epilogue, LoRA extension kept in bf16.
+bool lq_w8a8_supported(const lq_weight* w, int64_t n_tokens, int rank);
+size_t lq_w8a8_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank);
+void lq_w8a8_prepare_backward(const lq_weight* w, cudaStream_t st);
+void lq_w8a8_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, const float* B, int r, float s, void* Y,
+                 float* H_out, void* ws, size_t ws_bytes, cudaStream_t st);
+void lq_w8a8_bwd(const lq_weight* w, const void* dY, const void* X, const float* H, int64_t N, const float* A,
+                 const float* B, int r, float s, void* dX, float* dA, float* dB, int accumulate, void* ws,
+                 size_t ws_bytes, cudaStream_t st);

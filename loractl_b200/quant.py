@@ -110,6 +110,12 @@ class QuantWeight:
             L.check(L.lib().lq_weight_set_bias(self._h, b.data_ptr(), _stream_ptr(self.device)))
             torch.cuda.current_stream(self.device).synchronize()  # b may be a temporary
 
+    def prepare_fp8_backward(self) -> None:
+        """Builds the transposed e4m3 copy the native-fp8 backward reads, at load time, so the
+        step loop stays allocation-free (otherwise the first such backward builds it)."""
+        with torch.cuda.device(self.device):
+            L.check(L.lib().lq_weight_prepare_fp8_backward(self._h, _stream_ptr(self.device)))
+
     def unpack(self):
         """Logical content: (codes int8 [M,K], scales f32 [M,K/G]); for fp8, (bytes uint8 [M,K],
         scale f32 [1] or [M]).  Lets tests check bit-exactness independent of the tile layout."""
@@ -219,13 +225,25 @@ def _aligned(ws: torch.Tensor):
     return ws.data_ptr() + off, ws.numel() - off
 
 
+def _compute_code(t: torch.Tensor, fp8_compute: bool) -> int:
+    """dtype code of one call: the tensor's element type, or LQ_BF16_W8A8 when native fp8 compute
+    is requested (bf16 activations, scaled-fp8 weight)."""
+    dt = _dtype_code(t)
+    if fp8_compute:
+        if dt != L.LQ_BF16:
+            raise TypeError("native fp8 compute takes bf16 activations")
+        return L.LQ_BF16_W8A8
+    return dt
+
+
 def linear_fwd_raw(wq: QuantWeight, x2: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor],
-                   scaling: float, want_h: bool = True):
-    """Direct call of `lq_linear_fwd` on a flattened `[N, K]` activation.  Returns (y, h)."""
+                   scaling: float, want_h: bool = True, fp8_compute: bool = False):
+    """Direct call of `lq_linear_fwd` on a flattened `[N, K]` activation.  Returns (y, h).
+    `fp8_compute` selects LQ_BF16_W8A8 (tcgen05 e4m3 x e4m3; scaled-fp8 weights only)."""
     _require_cuda(x2, "x")
     n = x2.shape[0]
     rank = 0 if a is None else a.shape[1]
-    dt = _dtype_code(x2)
+    dt = _compute_code(x2, fp8_compute)
     y = torch.empty((n, wq.d_out), dtype=x2.dtype, device=x2.device)
     h = torch.empty((n, rank), dtype=torch.float32, device=x2.device) if (rank and want_h) else None
     with torch.cuda.device(x2.device):
@@ -242,12 +260,12 @@ def linear_bwd_raw(wq: QuantWeight, dy2: torch.Tensor, x2: Optional[torch.Tensor
                    a: Optional[torch.Tensor], b: Optional[torch.Tensor], scaling: float,
                    need_dx: bool = True, need_da: bool = True, need_db: bool = True,
                    da_out: Optional[torch.Tensor] = None, db_out: Optional[torch.Tensor] = None,
-                   accumulate: bool = False):
+                   accumulate: bool = False, fp8_compute: bool = False):
     """Direct call of `lq_linear_bwd`.  Returns (dx, da, db).  `da_out`/`db_out` let the caller
     point the gradients into a flat bucket (with `accumulate` to add instead of overwrite)."""
     n = dy2.shape[0]
     rank = 0 if a is None else a.shape[1]
-    dt = _dtype_code(dy2)
+    dt = _compute_code(dy2, fp8_compute)
     dev = dy2.device
     dx = torch.empty((n, wq.d_in), dtype=dy2.dtype, device=dev) if need_dx else None
     da = db = None
