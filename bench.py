@@ -278,6 +278,38 @@ def run_ours(args):
     lb.check_device_status(dev)
     kinds = {lib.lq_profile_kind_name(i).decode(): (ms_kind[i], int(cnt_kind[i])) for i in range(nk)}
 
+    # Scaled-fp8 workloads: also time the same step with native e4m3 MMA (LQ_BF16_W8A8), reported
+    # beside the headline under "native_fp8" (the headline itself stays the bf16-compute path).
+    native_fp8 = None
+    if scheme == "fp8" and not fp8c:
+        wq.prepare_fp8_backward()
+
+        def step8():
+            y8, h8 = Q.linear_fwd_raw(wq, x, a, b, s, fp8_compute=True)
+            Q.linear_bwd_raw(wq, dy, x, h8, a, b, s, da_out=da, db_out=db, fp8_compute=True)
+            if world > 1:
+                dist.all_reduce(bucket)
+
+        for _ in range(3):
+            step8()
+        lib.lq_profile_enable(1)
+        lib.lq_profile_collect(None, None, 0)
+        ms8 = timed(step8, args.steps)
+        ms_k8 = (C.c_double * nk)()
+        cnt_k8 = (C.c_uint64 * nk)()
+        lib.lq_profile_collect(ms_k8, cnt_k8, nk)
+        lib.lq_profile_enable(0)
+        lb.check_device_status(dev)
+        k8 = {lib.lq_profile_kind_name(i).decode(): (ms_k8[i], int(cnt_k8[i])) for i in range(nk)}
+        g8_ms, g8_n = k8.get("gemm_main", (0.0, 0))
+        native_fp8 = {
+            "value": step_flops(n, k, m, r) * world / (ms8 / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "ms_per_step": ms8 / args.steps, "dtype": "fp8 e4m3 x e4m3, f32 accumulate (bf16 in/out)",
+            "gemm_tflops": (main_gemm_flops(n, k, m, r) / 2) / (g8_ms / max(g8_n, 1) * 1e-3) / 1e12 if g8_n else None,
+            "by_kernel_ms_per_step": {kk: v[0] / args.steps for kk, v in k8.items() if v[1]},
+            "tolerance": "Y, dX within 5e-2 of peak vs the f32 oracle (tests/test_gpu_w8a8.py)",
+        }
+
     # The reference's dead-graph guards (crates/loractl-bench/src/lib.rs:35-104): twice the steps must
     # take about twice as long (ratio in [1.7, 2.3]) and the outputs must be finite and non-zero.
     ms_2x = timed(lambda: step(x, dy), 2 * args.steps)
@@ -403,6 +435,7 @@ def run_ours(args):
                     "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps},
             "gpu_launches": int(launches),
             "sanity": sanity,
+            "native_fp8": native_fp8,
             "model": {"step_flops": flops, "main_gemm_flops": main_gemm_flops(n, k, m, r),
                       "packed_stream_bytes": (k * m + 4 * m) if scheme == "fp8" else (k * m // 2 + 4 * k * m // group)},
             "clocks": clocks,
@@ -519,10 +552,100 @@ def run_stream(args):
     print(json.dumps(line))
 
 
+def run_train_step(args):
+    """`--regime step`: LoRA training steps/s of a double-stream MMDiT block stack (BASELINE configs
+    3 and 5: hidden 3072, 24 heads, MLP 12288, every linear int4 block-64 + LoRA, 4096 image + 512
+    text tokens per sample, bf16 activations, block-checkpoint recompute, flow-matching MSE loss),
+    data-parallel over the ranks torchrun started, LoRA gradients all-reduced in one flat bucket.
+    `--blocks` and `--batch` scale it down; the defaults are config 3 (one block, batch 1, rank 16)."""
+    import torch
+    import torch.distributed as dist
+
+    import loractl_b200 as lb
+    from loractl_b200 import _lib as L
+    from loractl_b200.harness import BlockConfig, BlockStack, Trainer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = BlockConfig()
+    n_blocks, lora_rank = args.blocks, args.rank
+    global_batch = max(args.batch, world)
+    lo, hi = lb.dp.shard_range(global_batch, rank, world)
+    b = hi - lo
+    stack = BlockStack(n_blocks, cfg, lora_rank, float(lora_rank), dev, seed=5)
+    trainer = Trainer(stack, lr=1e-4)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)  # per-rank data, identical weights
+    h = cfg.hidden
+    x0 = torch.randn((b, cfg.img_tokens, h), generator=g, device=dev, dtype=torch.bfloat16)
+    txt = torch.randn((b, cfg.txt_tokens, h), generator=g, device=dev, dtype=torch.bfloat16)
+    cond = torch.randn((b, h), generator=g, device=dev, dtype=torch.bfloat16)
+    noise = torch.randn(x0.shape, generator=g, device=dev, dtype=torch.bfloat16)
+    t = torch.rand((b,), generator=g, device=dev) * 0.9 + 0.05
+
+    def one():
+        return trainer.step(x0, txt, cond, t, noise)
+
+    losses = [one() for _ in range(max(args.warmup, 3))]
+    lb.check_device_status(dev)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches0 = L.lib().lq_kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        losses.append(one())
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        tm = torch.tensor([ms], device=dev)
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        ms = float(tm.item())
+    launches = L.lib().lq_kernel_launch_count() - launches0
+    lb.check_device_status(dev)
+    if rank == 0:
+        tokens = cfg.img_tokens + cfg.txt_tokens
+        p_stream = 4 * h * h + 2 * h * cfg.mlp
+        lin_fwd = 2 * tokens * p_stream + 2 * 2 * h * 6 * h  # both streams' projections + the two modulations
+        lora_fwd = 2 * tokens * lora_rank * (2 * h + 4 * h + 2 * h + 2 * (h + cfg.mlp))
+        att_fwd = 4 * tokens * tokens * h
+        flops_block = 2 * (lin_fwd + lora_fwd + att_fwd) + 2 * (lin_fwd + lora_fwd) + lora_fwd + 2 * att_fwd
+        step_fl = flops_block * n_blocks * global_batch
+        n_params = sum(p.numel() for p in stack.lora_parameters())
+        line = {
+            "metric": "MMDiT LoRA train steps/s", "value": args.steps / (ms * 1e-3), "unit": "steps/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "mmdit-double-stream", "blocks": n_blocks, "hidden": h, "heads": cfg.heads,
+                       "mlp": cfg.mlp, "lora_rank": lora_rank, "global_batch": global_batch,
+                       "tokens_per_sample": tokens, "quant": "int4 block 64", "grad_checkpointing": True,
+                       "parallelism": f"dp{world}"},
+            "model": {"step_flops": step_fl, "tflops": step_fl / (ms / args.steps * 1e-3) / 1e12,
+                      "lora_params": n_params, "grad_bucket_bytes": stack.flat.numel * 4},
+            "tokens_per_s": tokens * global_batch * args.steps / (ms * 1e-3),
+            "loss_first": losses[0], "loss_last": losses[-1], "gpu_launches": int(launches),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--regime", default="tensor", choices=["tensor", "stream"],
-                    help="tensor: the headline fwd+bwd step; stream: packed-weight stream at <= 64 tokens")
+    ap.add_argument("--blocks", type=int, default=1, help="--regime step: blocks in the stack (config 5: 24)")
+    ap.add_argument("--batch", type=int, default=1, help="--regime step: global batch (config 5: 8)")
+    ap.add_argument("--rank", type=int, default=16, help="--regime step: LoRA rank (config 5: 32)")
+    ap.add_argument("--regime", default="tensor", choices=["tensor", "stream", "step"],
+                    help="tensor: the headline fwd+bwd step; stream: packed-weight stream at <= 64 tokens; "
+                         "step: LoRA training steps/s of a double-stream MMDiT block stack")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
@@ -536,6 +659,8 @@ def main():
         run_reference(args)
     elif args.regime == "stream":
         run_stream(args)
+    elif args.regime == "step":
+        run_train_step(args)
     else:
         run_ours(args)
 

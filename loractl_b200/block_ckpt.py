@@ -18,7 +18,7 @@ import torch
 
 def checkpointed_step(blocks: Sequence[Callable[[torch.Tensor], torch.Tensor]], x0: torch.Tensor,
                       head_loss: Callable[[torch.Tensor], torch.Tensor], params: Iterable[torch.nn.Parameter],
-                      loss_scale: float = 1.0) -> Tuple[float, List[torch.Tensor]]:
+                      loss_scale: float = 1.0, keep_existing_grads: bool = False) -> Tuple[float, List[torch.Tensor]]:
     """One training step's loss and gradients with block-checkpoint recompute.
 
     blocks     the trunk, each `block(x) -> x` (adapters are closed over, as the reference passes
@@ -30,8 +30,9 @@ def checkpointed_step(blocks: Sequence[Callable[[torch.Tensor], torch.Tensor]], 
     quantities `(loss * loss_scale).backward()` of the monolithic step produces.
     """
     params = list(params)
-    for p in params:
-        p.grad = None
+    if not keep_existing_grads:  # with a flat gradient bucket the (zeroed) .grad views are kept and added into
+        for p in params:
+            p.grad = None
     # Phase 1 — capture (no graph)
     block_inputs: List[torch.Tensor] = []
     with torch.no_grad():

@@ -1,0 +1,184 @@
+"""Callers of the hot path, as PyTorch harnesses: a double-stream MMDiT block whose every linear
+is a LoRA'd quantized site, a stack of such blocks, and one data-parallel training step built
+from the pieces this package provides (site -> fused LoRA-linear kernels, block-checkpoint
+recompute, flat gradient bucket, bucket all-reduce, fused finite check and AdamW).
+
+The block follows the shape BASELINE's configs name — hidden 3072, 24 heads x 128, MLP 12288;
+per stream a joint-qkv 3072 -> 9216, out-projection 3072 -> 3072, MLP up 3072 -> 12288 / down
+12288 -> 3072 and an adaLN modulation 3072 -> 18432 on the conditioning vector — which is a
+synthetic composition: the reference's own denoiser is the single-stream Krea-2 DiT
+(crates/loractl-core/src/mmdit.rs:540-870), whose injectable sites this mirrors only in kind
+(`site()` at mmdit.rs:526-536 around each projection).  Attention, norms and activations are
+plain PyTorch ops (not kernels of this package); they are the callers either side of the path.
+
+The step mirrors crates/loractl-core/src/diffusion_trainer.rs:1599-1743 with
+`compute.grad_checkpointing` on: flow-matching inputs (crates/loractl-core/src/flow.rs:50-66),
+block-checkpointed forward/backward (block_ckpt.rs:103-207), finite-gradient guard with the
+dynamic loss scale, AdamW over the adapter set.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from . import dp
+from .adapters import LoraAdapters, LoraConfig, LoraSite, TargetSpec, build_adapters
+from .block_ckpt import checkpointed_step
+from .linear import BaseLinear, QuantLinear, site
+from .optim import AdamW, DynamicLossScale, FlatAdapters, nonfinite_flag
+from .quant import quantize_linear_weight
+
+
+@dataclass
+class BlockConfig:
+    hidden: int = 3072
+    heads: int = 24
+    mlp: int = 12288
+    img_tokens: int = 4096
+    txt_tokens: int = 512
+    quant_bits: int = 4
+    quant_block: int = 64
+
+
+def _quant_site(d_in: int, d_out: int, cfg: BlockConfig, gen: torch.Generator, device) -> BaseLinear:
+    """A frozen base linear with N(0, 0.02) weights, quantized on the device (the random-init
+    stand-in for `Mmdit::into_quantized`, crates/loractl-core/src/mmdit.rs:1122-1158)."""
+    w = torch.randn((d_out, d_in), generator=gen, device=device, dtype=torch.float32) * 0.02
+    return BaseLinear.quant(QuantLinear(quantize_linear_weight(w, cfg.quant_bits, cfg.quant_block)))
+
+
+class DoubleStreamBlock(nn.Module):
+    """One double-stream block; the block state is the concatenation [img tokens | txt tokens]
+    along the sequence axis so that block-checkpointing sees a single tensor."""
+
+    STREAMS = ("img", "txt")
+    LINEARS = ("mod", "qkv", "out", "up", "down")
+
+    def __init__(self, index: int, cfg: BlockConfig, gen: torch.Generator, device):
+        super().__init__()
+        self.index, self.cfg = index, cfg
+        h, m = cfg.hidden, cfg.mlp
+        dims = {"mod": (h, 6 * h), "qkv": (h, 3 * h), "out": (h, h), "up": (h, m), "down": (m, h)}
+        self.bases = nn.ModuleDict({f"{s}_{n}": _quant_site(*dims[n], cfg, gen, device)
+                                    for s in self.STREAMS for n in self.LINEARS})
+        self.adapters: Optional[LoraAdapters] = None
+        self.cond: Optional[torch.Tensor] = None  # [b, hidden] conditioning, set per step
+
+    def sites(self) -> List[LoraSite]:
+        return [LoraSite(self.path(s, n), self.bases[f"{s}_{n}"].d_in, self.bases[f"{s}_{n}"].d_out)
+                for s in self.STREAMS for n in self.LINEARS]
+
+    def path(self, stream: str, name: str) -> str:
+        return f"blocks.{self.index}.{stream}.{name}"
+
+    def _lin(self, stream: str, name: str, x: torch.Tensor) -> torch.Tensor:
+        return site(self.adapters, self.path(stream, name), self.bases[f"{stream}_{name}"], x)
+
+    def forward(self, state: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        b, _, h = state.shape
+        li = cfg.img_tokens
+        xs = {"img": state[:, :li], "txt": state[:, li:]}
+        cond = F.silu(self.cond.to(state.dtype))
+        mods, qkvs = {}, {}
+        for s in self.STREAMS:
+            mods[s] = self._lin(s, "mod", cond).unsqueeze(1).chunk(6, dim=-1)
+            shift, scale = mods[s][0], mods[s][1]
+            xn = F.layer_norm(xs[s], (h,)) * (1 + scale) + shift
+            qkvs[s] = self._lin(s, "qkv", xn).view(b, -1, 3, cfg.heads, h // cfg.heads)
+        qkv = torch.cat([qkvs["img"], qkvs["txt"]], dim=1)  # joint attention over both streams
+        q, k, v = (t.transpose(1, 2) for t in qkv.unbind(2))
+        att = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(b, -1, h)
+        atts = {"img": att[:, :li], "txt": att[:, li:]}
+        outs = []
+        for s in self.STREAMS:
+            _, _, gate1, shift2, scale2, gate2 = mods[s]
+            x = xs[s] + gate1 * self._lin(s, "out", atts[s])
+            xn = F.layer_norm(x, (h,)) * (1 + scale2) + shift2
+            x = x + gate2 * self._lin(s, "down", F.gelu(self._lin(s, "up", xn), approximate="tanh"))
+            outs.append(x)
+        return torch.cat(outs, dim=1)
+
+
+class BlockStack(nn.Module):
+    """`n_blocks` double-stream blocks with one LoRA adapter set over every linear."""
+
+    def __init__(self, n_blocks: int, cfg: BlockConfig, rank: int, alpha: float, device, seed: int = 5,
+                 dtype: torch.dtype = torch.bfloat16):
+        super().__init__()
+        gen = torch.Generator(device=device).manual_seed(seed)
+        self.cfg, self.dtype = cfg, dtype
+        self.blocks = nn.ModuleList(DoubleStreamBlock(i, cfg, gen, device) for i in range(n_blocks))
+        sites = [s for blk in self.blocks for s in blk.sites()]
+        lcfg = LoraConfig(rank=rank, alpha=alpha, targets=[TargetSpec(r"^blocks\.")])
+        torch.manual_seed(seed)  # identical adapters on every rank
+        self.adapters = build_adapters(sites, lcfg, device)
+        with torch.no_grad():  # non-zero B so that dA is exercised (crates/loractl-core/tests/block_ckpt.rs:69-71)
+            g2 = torch.Generator(device=device).manual_seed(seed + 1)
+            for d in self.adapters.deltas:
+                d.lora_b.copy_(torch.randn(d.lora_b.shape, generator=g2, device=device) * 0.01)
+        for blk in self.blocks:
+            blk.adapters = self.adapters
+        self.flat = FlatAdapters(self.adapters, device)
+
+    def lora_parameters(self):
+        return [p for d in self.adapters.deltas for p in (d.lora_a, d.lora_b)]
+
+    def set_cond(self, cond: torch.Tensor) -> None:
+        for blk in self.blocks:
+            blk.cond = cond
+
+    def forward(self, state: torch.Tensor) -> torch.Tensor:
+        for blk in self.blocks:
+            state = blk(state)
+        return state
+
+
+class Trainer:
+    """One rank of the data-parallel LoRA trainer over a `BlockStack`."""
+
+    def __init__(self, stack: BlockStack, lr: float = 1e-4, weight_decay: float = 1e-4, group=None,
+                 grad_checkpointing: bool = True):
+        self.stack, self.lr, self.group = stack, lr, group
+        self.optim = AdamW(stack.flat, weight_decay=weight_decay)
+        self.scaler = DynamicLossScale(initial=1.0)  # bf16/f32 gradients do not need the f16 head-room
+        self.grad_checkpointing = grad_checkpointing
+        self.steps_done = 0
+
+    def step(self, x0: torch.Tensor, txt: torch.Tensor, cond: torch.Tensor, t: torch.Tensor,
+             noise: torch.Tensor) -> float:
+        """x0 [b, L_img, h] clean latents, txt [b, L_txt, h], cond [b, h], t [b] in (0, 1), noise like x0.
+        Flow matching (crates/loractl-core/src/flow.rs:50-66): x_t = (1 - t) x0 + t eps, target
+        v = eps - x0, loss = mean((pred - v)^2) over the image tokens."""
+        stack, flat = self.stack, self.stack.flat
+        tt = t.view(-1, 1, 1).to(x0.dtype)
+        x_t = (1 - tt) * x0 + tt * noise
+        target = (noise - x0).float()
+        li = stack.cfg.img_tokens
+        stack.set_cond(cond)
+        state = torch.cat([x_t, txt], dim=1).to(stack.dtype)
+        head = lambda s: ((s[:, :li].float() - target) ** 2).mean()
+        flat.zero_grad()
+        params = stack.lora_parameters()
+        if self.grad_checkpointing:
+            loss, _ = checkpointed_step(list(stack.blocks), state, head, params, self.scaler.loss_scale,
+                                        keep_existing_grads=True)
+        else:
+            loss_t = head(stack(state))
+            (loss_t * self.scaler.loss_scale).backward()
+            loss = float(loss_t.detach())
+        flat.gather_autograd_grads()
+        nonfinite_flag(flat.grads, flat.flag)
+        scale = dp.sync_gradients(flat.grads, flat.flag, self.group)
+        # the optimizer reads the flag on the device and skips itself; the host reads it only to
+        # advance the loss-scale state (where the reference reads its |g| sum back)
+        self.optim.step(self.lr, grad_scale=scale / self.scaler.loss_scale, skip_flag=flat.flag)
+        finite, _ = dp.consensus_step(self.scaler, flat.flag)
+        if not finite:
+            self.optim.steps -= 1  # a skipped update does not advance the bias-correction clock
+        self.steps_done += 1
+        return loss
