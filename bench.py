@@ -617,7 +617,9 @@ def run_train_step(args):
         lin_fwd = 2 * tokens * p_stream + 2 * 2 * h * 6 * h  # both streams' projections + the two modulations
         lora_fwd = 2 * tokens * lora_rank * (2 * h + 4 * h + 2 * h + 2 * (h + cfg.mlp))
         att_fwd = 4 * tokens * tokens * h
-        flops_block = 2 * (lin_fwd + lora_fwd + att_fwd) + 2 * (lin_fwd + lora_fwd) + lora_fwd + 2 * att_fwd
+        # forward + recomputed forward + backward; the frozen weights get no gradient, so a linear's
+        # backward is dX only (1x its forward) plus the LoRA terms (2x); attention backward is 2x
+        flops_block = 2 * (lin_fwd + lora_fwd + att_fwd) + (lin_fwd + 2 * lora_fwd + 2 * att_fwd)
         step_fl = flops_block * n_blocks * global_batch
         n_params = sum(p.numel() for p in stack.lora_parameters())
         line = {
