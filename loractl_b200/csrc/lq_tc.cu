@@ -30,7 +30,7 @@ using namespace umma;
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quarter)
 
 struct GemmParams {
     int Mg, Ng;
@@ -45,6 +45,7 @@ struct GemmParams {
     const float* row_scale;
     const float* col_scale;
     int col_scale_bcast;
+    int tma_store;  // bf16 output leaves through shared memory and TMA tensor stores (full 64-byte row pieces)
 };
 
 template <int BLOCK_N>
@@ -54,7 +55,8 @@ struct Cfg {
     static constexpr int STAGES = (208 * 1024) / (A_BYTES + B_BYTES);
     // 2 accumulator stages; the allocation must be a power of two >= 32 columns
     static constexpr uint32_t TMEM_COLS = BLOCK_N * 2 <= 128 ? 128 : (BLOCK_N * 2 <= 256 ? 256 : 512);
-    static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr uint32_t STAGE_OUT = 8 * 2048;  // per epilogue warp: 32 rows x 64 bytes of bf16 output
+    static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + STAGE_OUT + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 __device__ __forceinline__ void item_coords(const GemmParams& p, int item, int& m_tile, int& n_tile, int& z) {
@@ -93,7 +95,8 @@ __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* dst, const 
 template <int BLOCK_N, bool A_MN, bool B_MN, typename OutT, bool F8 = false>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
-                 const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1, GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
+                 const __grid_constant__ CUtensorMap tmC, GemmParams p) {
     using C = Cfg<BLOCK_N>;
     constexpr int STAGES = C::STAGES;
     static_assert(!(F8 && (A_MN || B_MN)), "fp8 operands are K-major only");
@@ -102,7 +105,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + (size_t)STAGES * C::A_BYTES;
-    uint64_t* bars = (uint64_t*)(smem + (size_t)STAGES * (C::A_BYTES + C::B_BYTES));
+    uint8_t* stage_out = smem + (size_t)STAGES * (C::A_BYTES + C::B_BYTES);  // 1024-aligned
+    uint64_t* bars = (uint64_t*)(stage_out + C::STAGE_OUT);
     uint64_t* full = bars;
     uint64_t* empty = bars + STAGES;
     uint64_t* tfull = bars + 2 * STAGES;
@@ -119,7 +123,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&tfull[a]), 1);
-            mbar_init(smem_u32(&tempty[a]), 128);
+            mbar_init(smem_u32(&tempty[a]), 256);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -230,7 +234,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
         }
     } else {
         // ---------------- epilogue (warps 2..5) ----------------
-        const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+        const int quarter = warp & 3;       // TMEM lane quarter this warp may access
+        const int chalf = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -244,11 +249,65 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
             OutT* crow = Cbase + (long long)z * p.split_stride + (long long)row * p.ldc;
             const float rs = (p.row_scale && row < p.Mg) ? p.row_scale[row] : 1.f;
 #pragma unroll 1
-            for (int c = 0; c < BLOCK_N / 32; ++c) {
+            for (int c = 0; c < BLOCK_N / 64; ++c) {
                 uint32_t r[32];
-                tmem_ld_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N + c * 32), r);
+                const int cc = chalf * (BLOCK_N / 2) + c * 32;  // column of the tile this load starts at
+                tmem_ld_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N + cc), r);
                 tmem_ld_wait();
-                const int col0 = n_tile * BLOCK_N + c * 32;
+                const int col0 = n_tile * BLOCK_N + cc;
+                if (sizeof(OutT) == 2 && p.tma_store) {
+                    // scale / bias, round to bf16, stage the warp's 32 x 32 piece in shared memory in
+                    // the 64-byte-swizzled layout and hand it to a TMA tensor store: every row piece
+                    // leaves as one full 64-byte write instead of four 16-byte partial-sector writes
+                    // scattered over 32 rows (which measured 1.9 TB/s for an output-bound GEMM).
+                    uint32_t wds[16];
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        const int col = col0 + j;
+                        float v[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+                        if (col < p.Ng) {
+                            if (p.col_scale && !p.col_scale_bcast) {
+                                const float4 c0 = *(const float4*)(p.col_scale + col);
+                                const float4 c1 = *(const float4*)(p.col_scale + col + 4);
+                                const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) v[e] *= rs * cs[e];
+                            } else if (p.row_scale || p.col_scale) {
+                                const float sc = p.col_scale ? rs * p.col_scale[0] : rs;
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) v[e] *= sc;
+                            }
+                            if (p.bias) {
+                                const float4 b0 = *(const float4*)(p.bias + col);
+                                const float4 b1 = *(const float4*)(p.bias + col + 4);
+                                const float bs[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) v[e] += bs[e];
+                            }
+                        }
+#pragma unroll
+                        for (int e = 0; e < 8; e += 2) {
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[e], v[e + 1]);
+                            wds[(j + e) >> 1] = *(uint32_t*)&h2;
+                        }
+                    }
+                    uint8_t* my_stage = stage_out + (warp - 2) * 2048;
+                    if (lane == 0) bulk_wait_read0();  // the previous store has finished reading this buffer
+                    __syncwarp();
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)  // 16-byte chunk q of this lane's row, 64-byte swizzle
+                        *(uint4*)(my_stage + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) =
+                            make_uint4(wds[4 * q], wds[4 * q + 1], wds[4 * q + 2], wds[4 * q + 3]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tmC, smem_u32(my_stage), col0, m_tile * BM + quarter * 32);
+                        bulk_commit();
+                    }
+                    continue;
+                }
                 if (row < p.Mg) {
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
@@ -257,14 +316,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
                             float v[8];
 #pragma unroll
                             for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
-                            if (p.row_scale || p.col_scale) {
+                            if (p.col_scale && !p.col_scale_bcast) {  // col % 8 == 0: two aligned float4 loads
+                                const float4 c0 = *(const float4*)(p.col_scale + col);
+                                const float4 c1 = *(const float4*)(p.col_scale + col + 4);
+                                const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
-                                for (int e = 0; e < 8; ++e)
-                                    v[e] *= rs * (p.col_scale ? p.col_scale[p.col_scale_bcast ? 0 : col + e] : 1.f);
+                                for (int e = 0; e < 8; ++e) v[e] *= rs * cs[e];
+                            } else if (p.row_scale || p.col_scale) {
+                                const float sc = p.col_scale ? rs * p.col_scale[0] : rs;
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) v[e] *= sc;
                             }
                             if (p.bias) {
+                                const float4 b0 = *(const float4*)(p.bias + col);
+                                const float4 b1 = *(const float4*)(p.bias + col + 4);
+                                const float bs[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-                                for (int e = 0; e < 8; ++e) v[e] += p.bias[col + e];
+                                for (int e = 0; e < 8; ++e) v[e] += bs[e];
                             }
                             store8<OutT>(crow + col, v);
                         }
@@ -275,6 +343,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
             mbar_arrive(smem_u32(&tempty[acc]));
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
+        if (sizeof(OutT) == 2 && p.tma_store && lane == 0) bulk_wait0();  // stores complete before the CTA exits
     }
 
     tc_fence_before();
@@ -374,6 +443,23 @@ CUtensorMap make_map(const void* base, int64_t inner, int64_t rows, int64_t ld, 
     return m;
 }
 
+// bf16 output [rows, cols] (ld elements between rows): box 32 x 32, 64-byte swizzle, for TMA stores.
+CUtensorMap make_store_map(const void* base, int64_t cols, int64_t rows, int64_t ld) {
+    if (((uintptr_t)base & 15) != 0) throw LqError(LQ_ERR_INVALID, "tensor-core path: output must be 16-byte aligned");
+    if ((ld * 2) % 16 != 0) throw LqError(LQ_ERR_INVALID, "tensor-core path: output row stride must be a multiple of 16 bytes");
+    CUtensorMap m;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {32u, 32u};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        throw LqError(LQ_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult " + std::to_string((int)r));
+    return m;
+}
+
 struct DevCtx {
     int sm_count = 0;
     int* status = nullptr;
@@ -441,12 +527,16 @@ void launch_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand
     p.row_scale = sc.row;
     p.col_scale = sc.col;
     p.col_scale_bcast = sc.col_bcast;
+    // bf16 output (never split): 32 x 32 boxes, 64-byte swizzle, stored by TMA
+    p.tma_store = (sizeof(OutT) == 2 && splits == 1) ? 1 : 0;
+    CUtensorMap tC = tA0;
+    if (p.tma_store) tC = make_store_map(Cout, Ng, Mg, ldc);
     long long items = (long long)p.m_tiles * p.n_tiles * splits;
     int grid = (int)std::min<long long>(items, ctx.sm_count);
     auto kern = umma_gemm_kernel<BLOCK_N, A_MN, B_MN, OutT, F8>;
     LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
     LqProf prof(prof_kind, st);
-    kern<<<grid, kThreads, C::SMEM, st>>>(tA0, tB0, tA1, tB1, p);
+    kern<<<grid, kThreads, C::SMEM, st>>>(tA0, tB0, tA1, tB1, tC, p);
     LQ_CUDA(cudaGetLastError());
 }
 
@@ -1000,6 +1090,7 @@ void lq_tc_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B, int b_
                      float* partial_ws, const float* bias, cudaStream_t st) {
     Operand a{A, a_mn != 0, lda}, b{B, b_mn != 0, ldb};
     LQ_CHECK_ARG(Ng % 8 == 0 && ldc % 8 == 0, "gemm: Ng and ldc must be multiples of 8");
+    LQ_CHECK_ARG(((uintptr_t)bias & 15) == 0, "gemm: bias must be 16-byte aligned");
     if (splits > 1) {
         LQ_CHECK_ARG(c_dtype == LQ_F32 && partial_ws != nullptr && block_n == 64, "split gemm: f32 out, block_n 64");
         int64_t ldp = ((Ng + 63) / 64) * 64;
@@ -1113,12 +1204,13 @@ void launch_static_split(const void* A, int64_t lda, const void* B, int64_t ldb,
     p.row_scale = nullptr;
     p.col_scale = nullptr;
     p.col_scale_bcast = 0;
+    p.tma_store = 0;
     long long items = (long long)p.m_tiles * p.n_tiles * splits;
     int grid = (int)std::min<long long>(items, ctx.sm_count);
     auto kern = umma_gemm_kernel<64, MN, MN, float>;
     LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
     LqProf prof(LQ_K_GEMM_DOWN, st);
-    kern<<<grid, kThreads, C::SMEM, st>>>(tA, tB, tA, tB, p);
+    kern<<<grid, kThreads, C::SMEM, st>>>(tA, tB, tA, tB, tA, p);
     LQ_CUDA(cudaGetLastError());
 }
 
