@@ -268,7 +268,7 @@ def run_ours(args):
     lib.lq_profile_enable(1)
     lib.lq_profile_collect(None, None, 0)
     launches0 = lib.lq_kernel_launch_count()
-    total_ms = timed(lambda: step(x, dy), args.steps)
+    eager_ms = timed(lambda: step(x, dy), args.steps)
     launches = lib.lq_kernel_launch_count() - launches0
     nk = lib.lq_profile_kinds()
     ms_kind = (C.c_double * nk)()
@@ -277,6 +277,41 @@ def run_ours(args):
     lib.lq_profile_enable(0)
     lb.check_device_status(dev)
     kinds = {lib.lq_profile_kind_name(i).decode(): (ms_kind[i], int(cnt_kind[i])) for i in range(nk)}
+
+    # `value` is timed on a CUDA graph of the step (the library's launches are capturable: fixed
+    # workspace, tensor maps passed by value), replayed `steps` times, so that launch latency between
+    # the ~18 kernels of a step is not what is measured; the NCCL all-reduce stays outside the graph.
+    def capture(fn):
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            fn()  # sizes this stream's workspace before capture
+            with torch.cuda.graph(g, stream=side):
+                fn()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        return g
+
+    def local_step(f8):
+        y_, h_ = Q.linear_fwd_raw(wq, x, a, b, s, fp8_compute=f8)
+        Q.linear_bwd_raw(wq, dy, x, h_, a, b, s, da_out=da, db_out=db, fp8_compute=f8)
+
+    use_graph = not args.no_graph
+    if use_graph:
+        graph = capture(lambda: local_step(fp8c))
+
+        def graph_step():
+            graph.replay()
+            if world > 1:
+                dist.all_reduce(bucket)
+
+        for _ in range(3):
+            graph_step()
+        total_ms = timed(graph_step, args.steps)
+    else:
+        graph_step = lambda: step(x, dy)
+        total_ms = timed(graph_step, args.steps)
+    lb.check_device_status(dev)
 
     # Scaled-fp8 workloads: also time the same step with native e4m3 MMA (LQ_BF16_W8A8), reported
     # beside the headline under "native_fp8" (the headline itself stays the bf16-compute path).
@@ -294,13 +329,26 @@ def run_ours(args):
             step8()
         lib.lq_profile_enable(1)
         lib.lq_profile_collect(None, None, 0)
-        ms8 = timed(step8, args.steps)
+        timed(step8, args.steps)  # eager pass: per-kernel-class times
         ms_k8 = (C.c_double * nk)()
         cnt_k8 = (C.c_uint64 * nk)()
         lib.lq_profile_collect(ms_k8, cnt_k8, nk)
         lib.lq_profile_enable(0)
         lb.check_device_status(dev)
         k8 = {lib.lq_profile_kind_name(i).decode(): (ms_k8[i], int(cnt_k8[i])) for i in range(nk)}
+        if use_graph:
+            graph8 = capture(lambda: local_step(True))
+
+            def graph_step8():
+                graph8.replay()
+                if world > 1:
+                    dist.all_reduce(bucket)
+
+            for _ in range(3):
+                graph_step8()
+            ms8 = timed(graph_step8, args.steps)
+        else:
+            ms8 = timed(step8, args.steps)
         g8_ms, g8_n = k8.get("gemm_main", (0.0, 0))
         native_fp8 = {
             "value": step_flops(n, k, m, r) * world / (ms8 / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s",
@@ -312,7 +360,7 @@ def run_ours(args):
 
     # The reference's dead-graph guards (crates/loractl-bench/src/lib.rs:35-104): twice the steps must
     # take about twice as long (ratio in [1.7, 2.3]) and the outputs must be finite and non-zero.
-    ms_2x = timed(lambda: step(x, dy), 2 * args.steps)
+    ms_2x = timed(graph_step, 2 * args.steps)
     y_chk, dx_chk = step(x, dy)
     plausible = bool(torch.isfinite(y_chk).all() and torch.isfinite(dx_chk).all() and torch.isfinite(bucket).all()
                      and float(y_chk.float().abs().max()) > 0 and float(bucket.abs().max()) > 0)
@@ -416,7 +464,8 @@ def run_ours(args):
             "traffic_unit": "bytes per launch (ncu, full-size launch)",
             "algorithmic_bytes_per_launch": 2 * n * k + 2 * m * k + 2 * n * m,
             "launches_timed": gm_n, "avg_launch_ms": gm_ms / max(gm_n, 1),
-            "share_of_step": gm_ms / total_ms if total_ms else None,
+            "share_of_step": gm_ms / eager_ms if eager_ms else None,
+            "eager_ms_per_step": eager_ms / args.steps,
             "by_kernel_ms_per_step": {kk: v[0] / args.steps for kk, v in kinds.items() if v[1]},
         }
         cpu_tf, cpu_dt, cores = cpu_reference_rate(wl, min(n, 1024), 3)
@@ -427,7 +476,8 @@ def run_ours(args):
             "data": "synthetic",
             "config": {"workload": wl, "scheme": scheme, "d_in": k, "d_out": m, "rank": r, "alpha": alpha,
                        "tokens_per_gpu": n, "parallelism": f"dp{world}",
-                       "l2": "inputs larger than L2 (X+dY+Y+dX = 503 MB per step vs 126 MB)"},
+                       "l2": "inputs larger than L2 (X+dY+Y+dX = 503 MB per step vs 126 MB)",
+                       "launch": "eager" if args.no_graph else "CUDA graph of the step, replayed"},
             "roofline": roofline,
             "cpu_baseline": {"value": cpu_tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                              "sample": f"fwd+bwd on {min(n, 1024)} of {n} tokens, 3 reps, numpy f32"},
@@ -653,6 +703,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-graph", action="store_true",
+                    help="time eager launches instead of a CUDA graph of the step")
     ap.add_argument("--compute", default="bf16", choices=["bf16", "fp8"],
                     help="bf16: weights dequantised to bf16, bf16 MMA (parity-grade); fp8: native e4m3 MMA "
                          "on the stored fp8 weight with per-token e4m3 activations (scaled-fp8 workloads only)")
