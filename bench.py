@@ -501,7 +501,9 @@ def run_stream(args):
     of packed weights, more than the 126 MB L2) run back to back inside one CUDA graph, so every
     launch streams its weight from HBM and launch latency is not the thing measured.  Reports the
     algorithmic packed-stream bytes (K*M/2 + 4*K*M/64 = 5,308,416 B per site) per second, for
-    the whole site (H = X.A, fused GEMM, finalize) and for the fused kernel alone."""
+    the whole site (weight kernel with H = X.A folded in at N <= 16, finalize) and for the weight
+    kernel alone (stream_small_fwd_kernel, register dequant + mma.sync, at N <= 16;
+    fused_small_fwd_kernel, shared-memory dequant + tcgen05, above)."""
     import torch
 
     import loractl_b200 as lb
@@ -594,7 +596,7 @@ def run_stream(args):
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "cfg1-stream", "sites": sites, "d_in": k, "d_out": m, "rank": r,
                    "l2": "40 distinct weights = 212 MB > 126 MB L2", "launch": "CUDA graph replay"},
-        "roofline": {"bound": "hbm", "kernel": "fused_small_fwd_kernel", "achieved": best["fused_kernel_stream_gbs"],
+        "roofline": {"bound": "hbm", "kernel": "fused_small_fwd_kernel (64 tokens)", "achieved": best["fused_kernel_stream_gbs"],
                      "peak": hbm, "unit": "GB/s", "frac": best["fused_kernel_stream_gbs"] / hbm,
                      "algorithmic_bytes_per_launch": stream_bytes},
         "by_site": all_results,

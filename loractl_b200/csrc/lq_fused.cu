@@ -40,6 +40,12 @@ struct FusedParams {
     int m_tiles, splits;
     float* part;  // [splits][N][M]
     int* status;
+    // stream kernel only: the first `h_blocks` CTAs compute H = X . A (one token each) instead of
+    // weight items, so that the LoRA down-projection costs no launch of its own
+    int h_blocks, r, K;
+    const __nv_bfloat16* X;
+    const float* A;
+    float* H;
 };
 
 constexpr int KS = 4;  // k-tiles per pipeline stage: one bulk copy moves 4 packed tiles (16 KB)
@@ -278,6 +284,294 @@ fused_small_fwd_kernel(const __grid_constant__ CUtensorMap tmX, FusedParams p) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// N <= 16 tokens: register-dequant stream kernel.
+//
+// With so few tokens the tensor work per weight byte is tiny and the tcgen05 route above pays a
+// shared-memory round trip (packed -> bf16 operand tile) plus a fixed cost per MMA instruction.
+// Here the packed words go shared memory -> registers -> legacy warp MMA (mma.sync m16n8k16,
+// weights as the 16-row operand, 8 tokens as the narrow one) with nothing written back to shared
+// memory.  The instruction count per weight is what bounds this kernel, so the conversion is as
+// lean as the format allows: `(word >> 4j) & 0x000F000F | 0x43004300` is the bf16 pair
+// (128 + u, 128 + u') with u = q + 8, and it goes into the MMA as it is.  The excess
+// 136 * sum_k x[n, k] is the same for every weight row: one MMA with an all-ones operand yields
+// the token sums of the k-tile, and the accumulator of every row block starts from -136 times
+// them.  The group scale multiplies the f32 partial sum of its group instead of the weights, so
+// no weight is ever rounded (q exact, scale f32).
+//
+//   warp 0     producer, as above (one bulk copy of KS packed tiles, one of their scales, one
+//              3-D tensor copy of the KS X tiles [16 tokens][64 k], 128-byte swizzled)
+//   warps 1-4  consumers; warp w owns rows 32w .. 32w+31 of the 128-row tile (two m16 blocks)
+//
+// Fragment mapping.  The contraction index may be permuted freely as long as both operands use
+// the same permutation.  Lane (g = lane >> 2, t = lane & 3) reads, for rows g and g + 8 of a
+// block, word t (k = 8t .. 8t+7) and word 4 + t (k = 32 + 8t ..) of the row: each word feeds two
+// k16 steps, the pairs (e0,e1) | (e2,e3) then (e4,e5) | (e6,e7).  The matching X fragment is the
+// 16-byte chunk t (resp. 4 + t) of a token row, one LDS.128.  Steps 0-1 lie in k < 32 and steps
+// 2-3 in k >= 32, so a group of 32 never mixes with its neighbour.  Fragment column g holds token
+// (g >> 1) + 4 (g & 1) of its block of 8, which makes the swizzled X reads conflict-free.
+//
+// Partial tiles go to part[z][n][m] like the tcgen05 kernel's; fused_finalize_kernel sums the splits.
+// (Letting the CTA that arrives last at a tile finish Y in-kernel was measured: the counter reset plus
+// the serial tail cost more than the second launch saves at these sizes.)
+constexpr int kStreamThreads = 32 + 128;
+constexpr int STREAM_NT = 16;  // token rows of the X box
+constexpr uint32_t STREAM_X_BYTES = STREAM_NT * 128;
+constexpr uint32_t STREAM_RAW_BYTES = KS * (STREAM_X_BYTES + 4096 + 1024);
+constexpr int STREAM_STAGES = 2;
+constexpr size_t STREAM_SMEM = (size_t)STREAM_STAGES * STREAM_RAW_BYTES + 1024 + 128;
+constexpr int STREAM_CTAS_PER_SM = 3;
+
+__device__ __forceinline__ uint32_t dq_pair(uint32_t w, int sh) {
+    return ((w >> sh) & 0x000F000Fu) | 0x43004300u;  // (128 + u_lo, 128 + u_hi) as bf16
+}
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Two k16 steps: word `wg` of row g and `wh` of row g + 8 against the X chunk(s) `x`.
+template <int NB>
+__device__ __forceinline__ void half_mma(uint32_t wg, uint32_t wh, const uint4 (&x)[NB], float (&acc)[NB][4]) {
+    const uint32_t a0 = dq_pair(wg, 0), a1 = dq_pair(wh, 0), a2 = dq_pair(wg, 4), a3 = dq_pair(wh, 4);
+    const uint32_t c0 = dq_pair(wg, 8), c1 = dq_pair(wh, 8), c2 = dq_pair(wg, 12), c3 = dq_pair(wh, 12);
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+        mma_16816(acc[nb], a0, a1, a2, a3, x[nb].x, x[nb].y);
+        mma_16816(acc[nb], c0, c1, c2, c3, x[nb].z, x[nb].w);
+    }
+}
+
+// -136 * (sum of the 32 k of one X chunk pair), per token column of the fragment.
+template <int NB>
+__device__ __forceinline__ void half_offset(const uint4 (&x)[NB], float (&o)[NB][2], bool accumulate) {
+    constexpr uint32_t ONES = 0x3F803F80u;  // bf16 (1, 1)
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+        float one[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_16816(one, ONES, ONES, ONES, ONES, x[nb].x, x[nb].y);
+        mma_16816(one, ONES, ONES, ONES, ONES, x[nb].z, x[nb].w);
+        o[nb][0] = accumulate ? fmaf(-136.f, one[0], o[nb][0]) : -136.f * one[0];
+        o[nb][1] = accumulate ? fmaf(-136.f, one[1], o[nb][1]) : -136.f * one[1];
+    }
+}
+
+// H[n, :] = X[n, :] . A for one token by one CTA of kStreamThreads threads, f32 accumulation; 16
+// rank columns at a time, fixed shuffle tree then a fixed-order pass over the warps (deterministic).
+__device__ __forceinline__ void stream_h_block(const FusedParams& p, int n, float* red /* [5][16] */) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const __nv_bfloat16* x = p.X + (size_t)n * p.K;
+    for (int j0 = 0; j0 < p.r; j0 += 16) {
+        float acc[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+        const bool vec = (p.r - j0 >= 16) && (p.r % 4 == 0) && (((uintptr_t)p.A & 15) == 0);
+#pragma unroll 2
+        for (int k = tid; k < p.K; k += kStreamThreads) {
+            const float xv = __bfloat162float(x[k]);
+            const float* arow = p.A + (size_t)k * p.r + j0;
+            if (vec) {
+#pragma unroll
+                for (int j = 0; j < 16; j += 4) {
+                    const float4 a4 = *(const float4*)(arow + j);
+                    acc[j] = fmaf(xv, a4.x, acc[j]);
+                    acc[j + 1] = fmaf(xv, a4.y, acc[j + 1]);
+                    acc[j + 2] = fmaf(xv, a4.z, acc[j + 2]);
+                    acc[j + 3] = fmaf(xv, a4.w, acc[j + 3]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (j0 + j < p.r) acc[j] = fmaf(xv, arow[j], acc[j]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            float v = acc[j];
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+            if (lane == 0) red[warp * 16 + j] = v;
+        }
+        __syncthreads();
+        if (tid < 16 && j0 + tid < p.r) {
+            float h = 0.f;
+#pragma unroll
+            for (int w5 = 0; w5 < kStreamThreads / 32; ++w5) h += red[w5 * 16 + tid];
+            p.H[(size_t)n * p.r + j0 + tid] = h;
+        }
+        __syncthreads();
+    }
+}
+
+template <int NB>
+__global__ void __launch_bounds__(kStreamThreads, STREAM_CTAS_PER_SM)
+stream_small_fwd_kernel(const __grid_constant__ CUtensorMap tmX, FusedParams p) {
+    constexpr int RS = STREAM_STAGES;
+    extern __shared__ uint8_t smem_raw_[];
+    uint8_t* raw = (uint8_t*)(((uintptr_t)smem_raw_ + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(raw + (size_t)RS * STREAM_RAW_BYTES);
+    uint64_t* full_raw = bars;
+    uint64_t* empty_raw = bars + RS;
+    volatile int* abort_flag = (volatile int*)(bars + 2 * RS);
+
+    if ((int)blockIdx.x < p.h_blocks) {  // uniform per CTA
+        stream_h_block(p, (int)blockIdx.x, (float*)raw);
+        return;
+    }
+    const int first = (int)blockIdx.x - p.h_blocks, stride = (int)gridDim.x - p.h_blocks;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < RS; ++s) {
+            mbar_init(smem_u32(&full_raw[s]), 1);
+            mbar_init(smem_u32(&empty_raw[s]), 4);  // one arrival per consumer warp
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tmX);
+    }
+    __syncthreads();
+
+    const int num_items = p.m_tiles * p.splits;
+    const int gpt = 64 / p.group;
+    constexpr uint32_t X_OFF = 0, P_OFF = KS * STREAM_X_BYTES, S_OFF = P_OFF + KS * 4096;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int item = first; ok && item < num_items; item += stride) {
+                const int mt = item / p.splits, z = item - mt * p.splits;
+                const int kt0 = (int)(((long long)z * p.k_tiles) / p.splits);
+                const int kt1 = (int)(((long long)(z + 1) * p.k_tiles) / p.splits);
+                for (int kt = kt0; kt < kt1; kt += KS) {
+                    if (!mbar_wait(smem_u32(&empty_raw[s]), phase ^ 1u, abort_flag, p.status, 31)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(&full_raw[s]);
+                    const uint32_t base = smem_u32(raw + (size_t)s * STREAM_RAW_BYTES);
+                    const int tiles = min(KS, kt1 - kt);
+                    const uint32_t pk_bytes = (uint32_t)tiles * 4096u, sc_bytes = (uint32_t)(tiles * gpt) * 512u;
+                    mbar_expect_tx(bar, KS * STREAM_X_BYTES + pk_bytes + sc_bytes);  // the X box is always whole
+                    tma_load_3d(base + X_OFF, &tmX, bar, 0, 0, kt);
+                    bulk_load(base + P_OFF, p.packed + ((size_t)mt * p.k_tiles + kt) * 4096, pk_bytes, bar);
+                    bulk_load(base + S_OFF, p.scales + ((size_t)mt * p.n_groups + (size_t)kt * gpt) * 128, sc_bytes, bar);
+                    if (++s == RS) { s = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok)
+                for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    const int cw = warp - 1, g = lane >> 2, t = lane & 3;
+    const int tok = (g >> 1) + 4 * (g & 1);  // token (within a block of 8) held by fragment column g
+    const uint32_t x_lo_off = (uint32_t)tok * 128u + (((uint32_t)t ^ (uint32_t)tok) << 4);
+    const uint32_t x_hi_off = (uint32_t)tok * 128u + (((uint32_t)(4 + t) ^ (uint32_t)tok) << 4);
+    const uint32_t w_off = (uint32_t)((cw * 32 + g) * 8 + t);  // word index of (row g of block 0, word t)
+
+    int s = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int item = first; ok && item < num_items; item += stride) {
+        const int mt = item / p.splits, z = item - mt * p.splits;
+        const int kt0 = (int)(((long long)z * p.k_tiles) / p.splits);
+        const int kt1 = (int)(((long long)(z + 1) * p.k_tiles) / p.splits);
+        float tot[2][NB][4];
+#pragma unroll
+        for (int mb = 0; mb < 2; ++mb)
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) tot[mb][nb][e] = 0.f;
+        for (int kt = kt0; ok && kt < kt1; kt += KS) {
+            if (!mbar_wait(smem_u32(&full_raw[s]), phase, abort_flag, p.status, 32)) { ok = false; break; }
+            const int tiles = min(KS, kt1 - kt);
+            const uint8_t* stage = raw + (size_t)s * STREAM_RAW_BYTES;
+#pragma unroll 2
+            for (int j = 0; j < tiles; ++j) {
+                const uint8_t* xs = stage + X_OFF + j * STREAM_X_BYTES;
+                uint4 xlo[NB], xhi[NB];
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) {
+                    xlo[nb] = *(const uint4*)(xs + nb * 1024 + x_lo_off);
+                    xhi[nb] = *(const uint4*)(xs + nb * 1024 + x_hi_off);
+                }
+                const uint32_t* pk = (const uint32_t*)(stage + P_OFF + j * 4096) + w_off;
+                const float* sc = (const float*)(stage + S_OFF) + (size_t)(j * gpt) * 128 + cw * 32 + g;
+                float o_lo[NB][2], o_hi[NB][2];
+                half_offset<NB>(xlo, o_lo, false);
+                if (gpt == 2) {
+                    half_offset<NB>(xhi, o_hi, false);
+                } else {
+                    half_offset<NB>(xhi, o_lo, true);
+                }
+#pragma unroll
+                for (int mb = 0; mb < 2; ++mb) {
+                    const uint32_t wg0 = pk[mb * 128], wg1 = pk[mb * 128 + 4];
+                    const uint32_t wh0 = pk[mb * 128 + 64], wh1 = pk[mb * 128 + 68];
+                    float acc[NB][4];
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb) {
+                        acc[nb][0] = acc[nb][2] = o_lo[nb][0];
+                        acc[nb][1] = acc[nb][3] = o_lo[nb][1];
+                    }
+                    half_mma<NB>(wg0, wh0, xlo, acc);
+                    if (gpt == 2) {
+                        const float s0 = sc[mb * 16], s1 = sc[mb * 16 + 8];
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb) {
+                            tot[mb][nb][0] = fmaf(s0, acc[nb][0], tot[mb][nb][0]);
+                            tot[mb][nb][1] = fmaf(s0, acc[nb][1], tot[mb][nb][1]);
+                            tot[mb][nb][2] = fmaf(s1, acc[nb][2], tot[mb][nb][2]);
+                            tot[mb][nb][3] = fmaf(s1, acc[nb][3], tot[mb][nb][3]);
+                            acc[nb][0] = acc[nb][2] = o_hi[nb][0];
+                            acc[nb][1] = acc[nb][3] = o_hi[nb][1];
+                        }
+                    }
+                    half_mma<NB>(wg1, wh1, xhi, acc);
+                    const float* sc1 = sc + (gpt == 2 ? 128 : 0);
+                    const float s0 = sc1[mb * 16], s1 = sc1[mb * 16 + 8];
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb) {
+                        tot[mb][nb][0] = fmaf(s0, acc[nb][0], tot[mb][nb][0]);
+                        tot[mb][nb][1] = fmaf(s0, acc[nb][1], tot[mb][nb][1]);
+                        tot[mb][nb][2] = fmaf(s1, acc[nb][2], tot[mb][nb][2]);
+                        tot[mb][nb][3] = fmaf(s1, acc[nb][3], tot[mb][nb][3]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&empty_raw[s]));
+            if (++s == RS) { s = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        // partial tile of this item: fragment columns 2t, 2t+1 hold tokens t and t + 4 of the block
+        float* pz = p.part + (size_t)z * p.N * p.M;
+#pragma unroll
+        for (int mb = 0; mb < 2; ++mb) {
+            const int m0 = mt * 128 + cw * 32 + mb * 16 + g;
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                const int n0 = nb * 8 + t, n1 = n0 + 4;
+                if (m0 < p.M) {
+                    if (n0 < p.N) pz[(size_t)n0 * p.M + m0] = tot[mb][nb][0];
+                    if (n1 < p.N) pz[(size_t)n1 * p.M + m0] = tot[mb][nb][1];
+                }
+                if (m0 + 8 < p.M) {
+                    if (n0 < p.N) pz[(size_t)n0 * p.M + m0 + 8] = tot[mb][nb][2];
+                    if (n1 < p.N) pz[(size_t)n1 * p.M + m0 + 8] = tot[mb][nb][3];
+                }
+            }
+        }
+    }
+}
+
 // Second stage: Y[n, m] = bf16( sum_z part[z][n][m] + bias[m] + s * sum_j H[n, j] * B[j, m] ).
 __global__ void __launch_bounds__(256) fused_finalize_kernel(const float* __restrict__ part, int splits, int N, int M,
                                                              const float* __restrict__ bias,
@@ -398,6 +692,15 @@ void launch_fused(const CUtensorMap& tmX, const FusedParams& p, int grid, cudaSt
     LQ_CUDA(cudaGetLastError());
 }
 
+template <int NB>
+void launch_stream(const CUtensorMap& tmX, const FusedParams& p, int grid, cudaStream_t st) {
+    auto kern = stream_small_fwd_kernel<NB>;
+    LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)STREAM_SMEM));
+    LqProf prof(LQ_K_GEMM_MAIN, st);
+    kern<<<grid, kStreamThreads, STREAM_SMEM, st>>>(tmX, p);
+    LQ_CUDA(cudaGetLastError());
+}
+
 }  // namespace
 
 bool lq_fused_supported(const lq_weight* w, int64_t n_tokens, int rank) {
@@ -406,8 +709,10 @@ bool lq_fused_supported(const lq_weight* w, int64_t n_tokens, int rank) {
 
 size_t lq_fused_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank) {
     size_t h = al256((size_t)n_tokens * (size_t)(rank > 0 ? rank : 1) * 4);
-    size_t part = al256((size_t)16 * (size_t)n_tokens * (size_t)w->M * 4);
-    return h + part + 256;
+    size_t tok = (size_t)std::max<int64_t>(n_tokens, STREAM_NT);
+    size_t part = al256((size_t)16 * tok * (size_t)w->m_tiles * 128 * 4);
+    size_t counters = al256((size_t)w->m_tiles * 4);
+    return h + part + counters + 256;
 }
 
 void lq_fused_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, const float* B, int r, float s,
@@ -418,8 +723,9 @@ void lq_fused_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, 
     const int64_t M = w->M, K = w->K;
     float* Hf = (float*)ws;
     float* part = (float*)((char*)ws + al256((size_t)N * (size_t)(r > 0 ? r : 1) * 4));
-    if (r > 0) {  // H = X . A in f32: one block per token, a few MFLOP in total
-        if (H_out) Hf = H_out;
+    if (r > 0 && H_out) Hf = H_out;
+    const bool stream = N <= STREAM_NT;
+    if (r > 0 && !stream) {  // H = X . A in f32: one block per token, a few MFLOP in total
         LqProf prof(LQ_K_GEMM_DOWN, st);
         const __nv_bfloat16* Xb = (const __nv_bfloat16*)X;
         if (r <= 16) small_h_kernel<16><<<(unsigned)N, 256, 0, st>>>(Xb, A, (int)K, r, Hf);
@@ -437,15 +743,29 @@ void lq_fused_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, 
     p.n_groups = (int)w->n_groups;
     p.group = w->group;
     p.m_tiles = (int)w->m_tiles;
-    p.splits = pick_splits(p.m_tiles, p.k_tiles, sms);
     p.part = part;
     p.status = lq_tc_status_word(w->device);
-    const int grid = std::min(p.m_tiles * p.splits, sms);
-    const int nt = N <= 16 ? 16 : (N <= 32 ? 32 : 64);
-    CUtensorMap tmX = make_x_map3d(X, N, K, nt);
-    if (nt == 16) launch_fused<16>(tmX, p, grid, st);
-    else if (nt == 32) launch_fused<32>(tmX, p, grid, st);
-    else launch_fused<64>(tmX, p, grid, st);
+    p.h_blocks = (stream && r > 0) ? (int)N : 0;
+    p.r = r;
+    p.K = (int)K;
+    p.X = (const __nv_bfloat16*)X;
+    p.A = A;
+    p.H = Hf;
+    if (stream) {  // register-dequant stream kernel, several small CTAs per SM
+        const int slots = sms * STREAM_CTAS_PER_SM - p.h_blocks;
+        p.splits = pick_splits(p.m_tiles, p.k_tiles, slots);
+        const int grid = std::min(p.m_tiles * p.splits, slots) + p.h_blocks;
+        CUtensorMap tmX = make_x_map3d(X, N, K, STREAM_NT);
+        if (N <= 8) launch_stream<1>(tmX, p, grid, st);
+        else launch_stream<2>(tmX, p, grid, st);
+    } else {
+        p.splits = pick_splits(p.m_tiles, p.k_tiles, sms);
+        const int grid = std::min(p.m_tiles * p.splits, sms);
+        const int nt = N <= 32 ? 32 : 64;
+        CUtensorMap tmX = make_x_map3d(X, N, K, nt);
+        if (nt == 32) launch_fused<32>(tmX, p, grid, st);
+        else launch_fused<64>(tmX, p, grid, st);
+    }
     {
         LqProf prof(LQ_K_REDUCE, st);
         dim3 g((unsigned)((M + 255) / 256), (unsigned)N);
