@@ -5,8 +5,12 @@
 //   C[Mg, Ng] = A[Mg, Kg] . B[Ng, Kg]^T          (bf16 operands, f32 accumulation in TMEM)
 //
 //   warp 0 : TMA producer   (cp.async.bulk.tensor 2-D tiles, 128-byte swizzle, no multicast)
-//   warp 1 : MMA issuer     (tcgen05.mma cta_group::1, 128 x BLOCK_N x 16 per instruction)
-//   warps 2-5 : epilogue    (tcgen05.ld from TMEM -> registers -> global)
+//   warp 1 : MMA issuer     (tcgen05.mma cta_group::1, 128 x BLOCK_N x 16 per instruction;
+//                            kind::f16 on bf16 operands, kind::f8f6f4 on e4m3 operands)
+//   warps 2-9 : epilogue    (tcgen05.ld from TMEM -> registers; two warps per TMEM lane quarter,
+//                            each draining half of the columns; scales and bias applied here;
+//                            bf16 output is staged in shared memory, 64-byte swizzled, and leaves
+//                            through TMA tensor stores, f32 partial tiles through plain stores)
 //
 // The K loop may continue into a second pair of tensor maps ("K extension").  That is how
 // the rank-r LoRA product is fused into the frozen GEMM: with A1 = s*H (N x r, zero padded to
