@@ -38,6 +38,9 @@ WORKLOADS = {
     # name: (scheme, K = d_in, M = d_out, rank, alpha, tokens, group)
     "cfg2": ("fp8", 3072, 12288, 32, 32.0, 8192, 0),
     "cfg1": ("int4", 3072, 3072, 16, 16.0, 4096, 64),
+    # the MLP up-projection of BASELINE config 3's block, int4 block 64, rank 16, on the block's
+    # 4096 image + 512 text tokens
+    "cfg3up": ("int4", 3072, 12288, 16, 16.0, 4608, 64),
 }
 METRIC = "LoRA-linear fwd+bwd TFLOP/s"
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of the dominant kernel, from
@@ -476,7 +479,7 @@ def run_ours(args):
             "data": "synthetic",
             "config": {"workload": wl, "scheme": scheme, "d_in": k, "d_out": m, "rank": r, "alpha": alpha,
                        "tokens_per_gpu": n, "parallelism": f"dp{world}",
-                       "l2": "inputs larger than L2 (X+dY+Y+dX = 503 MB per step vs 126 MB)",
+                       "l2": f"inputs larger than L2 (X+dY+Y+dX = {4 * n * (k + m) / 1e6:.0f} MB per step vs 126 MB)",
                        "launch": "eager" if args.no_graph else "CUDA graph of the step, replayed"},
             "roofline": roofline,
             "cpu_baseline": {"value": cpu_tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",

@@ -19,6 +19,8 @@
 //
 // Work items are (output tile, k-split); with splits > 1 the kernel writes f32 partial tiles
 // that a fixed-order second stage reduces (deterministic: no atomics anywhere).
+#include <cstdlib>
+#include <map>
 #include <mutex>
 #include <vector>
 
@@ -464,16 +466,32 @@ CUtensorMap make_store_map(const void* base, int64_t cols, int64_t rows, int64_t
     return m;
 }
 
+// Fork-join helper objects of one caller stream: the steps of a forward or backward that do not
+// depend on each other (weight dequantisation and operand casts on one side, the LoRA down
+// projection on the other; dA and dB) are enqueued on a second stream between an event fork and
+// an event join, so that their launch latencies overlap instead of adding up.  Both the eager
+// path and a stream capture of the call see an ordinary fork-join (the side stream joins the
+// capture through the fork event and is joined back before the call returns).
+struct Fork {
+    cudaStream_t side = nullptr;
+    cudaEvent_t ev_fork = nullptr;
+    cudaEvent_t ev_join[2] = {nullptr, nullptr};
+};
+
 struct DevCtx {
     int sm_count = 0;
     int* status = nullptr;
+    std::mutex fork_mu;
+    std::map<cudaStream_t, Fork> forks;
 };
+
+constexpr int kMaxDevices = 64;
 
 DevCtx& dev_ctx(int dev) {
     static std::mutex mu;
-    static std::vector<DevCtx> ctx;
+    static DevCtx ctx[kMaxDevices];  // fixed storage: references stay valid
+    if (dev < 0 || dev >= kMaxDevices) throw LqError(LQ_ERR_INVALID, "device index out of range");
     std::lock_guard<std::mutex> lk(mu);
-    if ((int)ctx.size() <= dev) ctx.resize(dev + 1);
     DevCtx& c = ctx[dev];
     if (!c.status) {
         LQ_CUDA(cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev));
@@ -482,6 +500,58 @@ DevCtx& dev_ctx(int dev) {
     }
     return c;
 }
+
+bool fork_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("LQ_SERIAL_LAUNCH");
+        return !(e && e[0] == '1');
+    }();
+    return on;
+}
+
+// One Fork per (device, caller stream), created on first use.  Creation happens with the thread's
+// capture mode relaxed, so a first call made under a global-mode stream capture still works.
+Fork& fork_for(DevCtx& c, cudaStream_t st) {
+    std::lock_guard<std::mutex> lk(c.fork_mu);
+    auto it = c.forks.find(st);
+    if (it != c.forks.end()) return it->second;
+    cudaStreamCaptureMode mode = cudaStreamCaptureModeRelaxed;
+    LQ_CUDA(cudaThreadExchangeStreamCaptureMode(&mode));
+    Fork f;
+    cudaError_t e = cudaStreamCreateWithFlags(&f.side, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&f.ev_fork, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&f.ev_join[0], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&f.ev_join[1], cudaEventDisableTiming);
+    cudaThreadExchangeStreamCaptureMode(&mode);
+    if (e != cudaSuccess) throw LqError(LQ_ERR_CUDA, std::string("fork-join objects: ") + cudaGetErrorString(e));
+    return c.forks.emplace(st, f).first->second;
+}
+
+// `side()` is the second stream after `fork()`, or the caller's stream itself when forking is off.
+struct ForkJoin {
+    Fork* f = nullptr;
+    cudaStream_t main_st;
+    ForkJoin(DevCtx& c, cudaStream_t st, bool want) : main_st(st) {
+        if (want && fork_enabled()) f = &fork_for(c, st);
+    }
+    cudaStream_t side() const { return f ? f->side : main_st; }
+    void fork() {
+        if (!f) return;
+        LQ_CUDA(cudaEventRecord(f->ev_fork, main_st));
+        LQ_CUDA(cudaStreamWaitEvent(f->side, f->ev_fork, 0));
+    }
+    // record(i): marks the point the side stream has reached; wait(i): the caller's stream waits for it
+    void record(int i) {
+        if (f) LQ_CUDA(cudaEventRecord(f->ev_join[i], f->side));
+    }
+    void wait(int i) {
+        if (f) LQ_CUDA(cudaStreamWaitEvent(main_st, f->ev_join[i], 0));
+    }
+    void join(int i) {
+        record(i);
+        wait(i);
+    }
+};
 
 struct Operand {
     const void* ptr;  // bf16
@@ -564,6 +634,8 @@ struct TcWs {
     __nv_bfloat16* pdown; // fwd: A^T [r, K]         bwd: B [r, M]
     __nv_bfloat16* pext;  // fwd: B^T [M, EXT]       bwd: A [K, EXT]
     float* part;          // split partials
+    float* part2;         // split partials of the contractions that run on the side stream (dB, recomputed H)
+    __nv_bfloat16* pdown2; // bwd, H recomputed: A^T [r, K]
     size_t bytes;
 };
 
@@ -588,6 +660,8 @@ TcWs carve_tc(const lq_weight* w, int64_t N, int r, void* base, int sm_count) {
         size_t rows = std::max((size_t)N, std::max(M, K));
         (void)sm_count;
         t.part = (float*)take((size_t)16 * rows * EXT * 4);
+        t.part2 = (float*)take((size_t)16 * rows * EXT * 4);
+        t.pdown2 = (__nv_bfloat16*)take((size_t)r * K * 2);
     }
     t.bytes = al256(off);
     return t;
@@ -596,7 +670,7 @@ TcWs carve_tc(const lq_weight* w, int64_t N, int r, void* base, int sm_count) {
 // Out[I, r] = alpha * Z[I, C] . P[r, C]^T  via split-K tcgen05 GEMM + fixed-order reduce.
 void skinny_down(const void* Z, int64_t I, int64_t Cdim, int64_t ldz, const __nv_bfloat16* P, int64_t ldp_in, int r,
                  float alpha, float* out_f32, __nv_bfloat16* ext, float ext_scale, float* part, int sm_count,
-                 cudaStream_t st, const float* ext_row_div = nullptr) {
+                 cudaStream_t st, const float* ext_row_div = nullptr, ForkJoin* wait_before_reduce = nullptr) {
     const int EXT = ext_width(r);
     const int64_t kb = (Cdim + BK - 1) / BK;
     const int64_t m_tiles = (I + BM - 1) / BM, n_tiles = EXT / 64;
@@ -605,6 +679,7 @@ void skinny_down(const void* Z, int64_t I, int64_t Cdim, int64_t ldz, const __nv
     launch_gemm<64, false, false, float>(a, b, Cdim, nullptr, nullptr, 0, part, EXT, I * (int64_t)EXT, I, EXT, splits,
                                          nullptr, st, r, LQ_K_GEMM_DOWN);
     long long total = (long long)I * EXT;
+    if (wait_before_reduce) wait_before_reduce->wait(0);  // `ext_row_div` is produced on the side stream
     LqProf prof(LQ_K_REDUCE, st);
     reduce_partials_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(part, I * (long long)EXT, splits, EXT, I, r,
                                                                           EXT, alpha, out_f32, r, 0, 0, ext, EXT,
@@ -811,6 +886,8 @@ struct W8Ws {
     __nv_bfloat16* pdown; // A^T [r, K] / B [r, M]
     __nv_bfloat16* pext;  // B^T [M, EXT] / A [K, EXT]
     float* part;
+    float* part2;          // partials of the contractions on the side stream (dB, recomputed H)
+    __nv_bfloat16* pdown2; // bwd, H recomputed: A^T [r, K]
     size_t bytes;
 };
 
@@ -835,6 +912,8 @@ W8Ws carve_w8(const lq_weight* w, int64_t N, int r, void* base) {
         t.pdown = (__nv_bfloat16*)take((size_t)r * std::max(M, K) * 2);
         t.pext = (__nv_bfloat16*)take(std::max(M, K) * EXT * 2);
         t.part = (float*)take((size_t)16 * std::max((size_t)N, std::max(M, K)) * EXT * 4);
+        t.part2 = (float*)take((size_t)16 * std::max((size_t)N, std::max(M, K)) * EXT * 4);
+        t.pdown2 = (__nv_bfloat16*)take((size_t)r * K * 2);
     }
     t.bytes = al256(off);
     return t;
@@ -932,20 +1011,25 @@ void lq_tc_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, con
     if (t.bytes > ws_bytes)
         throw LqError(LQ_ERR_WORKSPACE, "workspace too small: need " + std::to_string(t.bytes) + " bytes, got " +
                                             std::to_string(ws_bytes));
-    // 1. frozen weight -> bf16 scratch [M, K] (rounds q*scale, resp. LUT*scale, once to bf16)
-    lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, st);
     Operand a0{X, false, K}, b0{t.wscr, false, K};
     if (r == 0) {
+        lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, st);
         main_gemm<__nv_bfloat16>(a0, b0, K, nullptr, nullptr, 0, (__nv_bfloat16*)Y, M, N, M, w->bias, ctx.sm_count, st);
         return;
     }
     const int EXT = ext_width(r);
-    // 2. H = X . A  (f32 [N, r] for the backward; bf16 s*H, zero padded, as the K extension)
+    ForkJoin fj(ctx, st, true);
+    fj.fork();
+    // side: frozen weight -> bf16 scratch [M, K] (rounds q*scale, resp. LUT*scale, once to bf16),
+    //       and B^T [M, EXT] for the K extension
+    lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, fj.side());
+    cast_pad(B, 1, M, t.pext, EXT, M, r, EXT, 1.f, fj.side());
+    // main: H = X . A  (f32 [N, r] for the backward; bf16 s*H, zero padded, as the K extension)
     cast_pad(A, 1, r, t.pdown, K, r, (int)K, (int)K, 1.f, st);  // A^T [r, K]
     float* Hf = H_out ? H_out : t.Hf;
     skinny_down(X, N, K, K, t.pdown, K, r, 1.f, Hf, t.ext_a, s, t.part, ctx.sm_count, st);
-    // 3. Y = [X | s*H] . [W | B^T]^T + bias
-    cast_pad(B, 1, M, t.pext, EXT, M, r, EXT, 1.f, st);  // B^T [M, EXT]
+    fj.join(0);
+    // Y = [X | s*H] . [W | B^T]^T + bias
     Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
     main_gemm<__nv_bfloat16>(a0, b0, K, &a1, &b1, EXT, (__nv_bfloat16*)Y, M, N, M, w->bias, ctx.sm_count, st);
 }
@@ -962,32 +1046,44 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
         throw LqError(LQ_ERR_WORKSPACE, "workspace too small: need " + std::to_string(t.bytes) + " bytes, got " +
                                             std::to_string(ws_bytes));
     const int EXT = ext_width(r > 0 ? r : 1);
-    if (dX) lq_launch_dequant(w, t.wscr, LQ_BF16, M, 1, st);  // W^T [K, M]
     Operand a0{dY, false, M}, b0{t.wscr, false, M};
     if (r == 0) {
-        if (dX) main_gemm<__nv_bfloat16>(a0, b0, M, nullptr, nullptr, 0, (__nv_bfloat16*)dX, K, N, K, nullptr, ctx.sm_count, st);
+        if (dX) {
+            lq_launch_dequant(w, t.wscr, LQ_BF16, M, 1, st);  // W^T [K, M]
+            main_gemm<__nv_bfloat16>(a0, b0, M, nullptr, nullptr, 0, (__nv_bfloat16*)dX, K, N, K, nullptr, ctx.sm_count, st);
+        }
         return;
     }
-    // dH = s * dY . B^T   (f32 [N, r]; bf16 copy as the K extension of the dX GEMM and as dA's operand)
+    ForkJoin fj(ctx, st, true);
+    fj.fork();
+    // side: what the dX GEMM needs besides dH: W^T [K, M] and A [K, EXT] in bf16
+    if (dX) {
+        lq_launch_dequant(w, t.wscr, LQ_BF16, M, 1, fj.side());
+        cast_pad(A, r, 1, t.pext, EXT, K, r, EXT, 1.f, fj.side());
+    }
+    fj.record(0);  // the caller's stream waits for this point just before the dX GEMM
+    // side, continued (independent of everything on the caller's stream): dB[r, M] = (s*H)^T . dY
+    if (dB) {
+        const float* Hsrc = H;
+        if (!Hsrc) {  // H not kept by the caller: recompute it (own cast buffer: pdown holds B meanwhile)
+            cast_pad(A, 1, r, t.pdown2, K, r, (int)K, (int)K, 1.f, fj.side());
+            skinny_down(X, N, K, K, t.pdown2, K, r, 1.f, t.Hf, t.ext_b, s, t.part2, ctx.sm_count, fj.side());
+        } else {
+            cast_pad(Hsrc, r, 1, t.ext_b, EXT, N, r, EXT, s, fj.side());
+        }
+        skinny_grad(dY, N, M, M, t.ext_b, r, 1.f, dB, 1, accumulate, t.part2, ctx.sm_count, fj.side());
+    }
+    // main: dH = s * dY . B^T   (f32 [N, r]; bf16 copy as the K extension of the dX GEMM and as dA's operand)
     cast_pad(B, M, 1, t.pdown, M, r, (int)M, (int)M, 1.f, st);  // B as bf16 [r, M]
     skinny_down(dY, N, M, M, t.pdown, M, r, s, t.dHf, t.ext_a, 1.f, t.part, ctx.sm_count, st);
     if (dX) {  // dX = [dY | dH] . [W^T | A]^T
-        cast_pad(A, r, 1, t.pext, EXT, K, r, EXT, 1.f, st);  // A [K, EXT]
+        fj.wait(0);
         Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
         main_gemm<__nv_bfloat16>(a0, b0, M, &a1, &b1, EXT, (__nv_bfloat16*)dX, K, N, K, nullptr, ctx.sm_count, st);
     }
     if (dA)  // dA[K, r] = X^T . dH
         skinny_grad(X, N, K, K, t.ext_a, r, 1.f, dA, 0, accumulate, t.part, ctx.sm_count, st);
-    if (dB) {  // dB[r, M] = (s*H)^T . dY
-        const float* Hsrc = H;
-        if (!Hsrc) {
-            cast_pad(A, 1, r, t.pdown, K, r, (int)K, (int)K, 1.f, st);
-            skinny_down(X, N, K, K, t.pdown, K, r, 1.f, t.Hf, t.ext_b, s, t.part, ctx.sm_count, st);
-        } else {
-            cast_pad(Hsrc, r, 1, t.ext_b, EXT, N, r, EXT, s, st);
-        }
-        skinny_grad(dY, N, M, M, t.ext_b, r, 1.f, dB, 1, accumulate, t.part, ctx.sm_count, st);
-    }
+    fj.join(1);
 }
 
 // ---- native fp8 (w8a8) entry points ------------------------------------------------------
@@ -1014,24 +1110,29 @@ void lq_w8a8_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, c
         throw LqError(LQ_ERR_WORKSPACE, "workspace too small: need " + std::to_string(t.bytes) + " bytes, got " +
                                             std::to_string(ws_bytes));
     const bool per_channel = w->scale_kind == LQ_SCALE_PER_CHANNEL;
-    // 1. X -> e4m3 with one scale per token
-    quant_rows(X, N, K, nullptr, t.q8, t.srow, st);
     EpiScales sc;
     sc.row = t.srow;
     sc.col = w->scales;
     sc.col_bcast = per_channel ? 0 : 1;
     Operand a0{t.q8, false, K}, b0{w->packed, false, K};
     if (r == 0) {
+        quant_rows(X, N, K, nullptr, t.q8, t.srow, st);  // X -> e4m3 with one scale per token
         main_gemm_f8(a0, b0, K, nullptr, nullptr, 0, (__nv_bfloat16*)Y, M, N, M, w->bias, sc, ctx.sm_count, st);
         return;
     }
     const int EXT = ext_width(r);
-    // 2. H = X . A (bf16 operands, f32 out); extension operand s*H / s_x[n]
+    ForkJoin fj(ctx, st, true);
+    fj.fork();
+    // side: X -> e4m3 with one scale per token; B^T / s_w[m] for the K extension
+    quant_rows(X, N, K, nullptr, t.q8, t.srow, fj.side());
+    cast_pad(B, 1, M, t.pext, EXT, M, r, EXT, 1.f, fj.side(), w->scales, per_channel ? 0 : 1);
+    fj.record(0);
+    // main: H = X . A (bf16 operands, f32 out); extension operand s*H / s_x[n] (the reduce waits for s_x)
     cast_pad(A, 1, r, t.pdown, K, r, (int)K, (int)K, 1.f, st);
     float* Hf = H_out ? H_out : t.Hf;
-    skinny_down(X, N, K, K, t.pdown, K, r, 1.f, Hf, t.ext_a, s, t.part, ctx.sm_count, st, t.srow);
-    // 3. B^T / s_w[m], then Y = (X8 . W8^T + ext) * s_x[n] * s_w[m] + bias
-    cast_pad(B, 1, M, t.pext, EXT, M, r, EXT, 1.f, st, w->scales, per_channel ? 0 : 1);
+    skinny_down(X, N, K, K, t.pdown, K, r, 1.f, Hf, t.ext_a, s, t.part, ctx.sm_count, st, t.srow, &fj);
+    fj.wait(0);
+    // Y = (X8 . W8^T + ext) * s_x[n] * s_w[m] + bias
     Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
     main_gemm_f8(a0, b0, K, &a1, &b1, EXT, (__nv_bfloat16*)Y, M, N, M, w->bias, sc, ctx.sm_count, st);
 }
@@ -1048,25 +1149,47 @@ void lq_w8a8_bwd(const lq_weight* w, const void* dY, const void* X, const float*
                                             std::to_string(ws_bytes));
     const bool per_channel = w->scale_kind == LQ_SCALE_PER_CHANNEL;
     const int EXT = ext_width(r > 0 ? r : 1);
-    const uint8_t* wt = nullptr;
     EpiScales sc;
     if (dX) {
-        wt = ensure_transposed(w, st);
-        // dY' = dY * s_w[m] (per-channel scale folded in: it lies on the reduction axis), then e4m3 per token
-        quant_rows(dY, N, M, per_channel ? w->scales : nullptr, t.q8, t.srow, st);
         sc.row = t.srow;
         if (!per_channel) { sc.col = w->scales; sc.col_bcast = 1; }
     }
-    Operand a0{t.q8, false, M}, b0{wt, false, M};
     if (r == 0) {
-        if (dX) main_gemm_f8(a0, b0, M, nullptr, nullptr, 0, (__nv_bfloat16*)dX, K, N, K, nullptr, sc, ctx.sm_count, st);
+        if (dX) {
+            const uint8_t* wt = ensure_transposed(w, st);
+            quant_rows(dY, N, M, per_channel ? w->scales : nullptr, t.q8, t.srow, st);
+            Operand a0{t.q8, false, M}, b0{wt, false, M};
+            main_gemm_f8(a0, b0, M, nullptr, nullptr, 0, (__nv_bfloat16*)dX, K, N, K, nullptr, sc, ctx.sm_count, st);
+        }
         return;
     }
-    // dH = s * dY . B^T from the bf16 dY; extension operand dH / s_dy[n] (and / s_w when that is a scalar)
-    cast_pad(B, M, 1, t.pdown, M, r, (int)M, (int)M, 1.f, st);
-    skinny_down(dY, N, M, M, t.pdown, M, r, s, t.dHf, t.ext_a, 1.f, t.part, ctx.sm_count, st, dX ? t.srow : nullptr);
+    ForkJoin fj(ctx, st, true);
+    fj.fork();
+    const uint8_t* wt = nullptr;
     if (dX) {
-        cast_pad(A, r, 1, t.pext, EXT, K, r, EXT, 1.f, st, per_channel ? nullptr : w->scales, 1);
+        // side: dY' = dY * s_w[m] (per-channel scale folded in: it lies on the reduction axis), then e4m3
+        // per token; A [K, EXT] (/ s_w when that is a scalar) for the K extension
+        wt = ensure_transposed(w, fj.side());
+        quant_rows(dY, N, M, per_channel ? w->scales : nullptr, t.q8, t.srow, fj.side());
+        cast_pad(A, r, 1, t.pext, EXT, K, r, EXT, 1.f, fj.side(), per_channel ? nullptr : w->scales, 1);
+    }
+    fj.record(0);
+    if (dB) {  // side, continued: dB = (s*H)^T . dY, independent of everything on the caller's stream
+        if (!H) {
+            cast_pad(A, 1, r, t.pdown2, K, r, (int)K, (int)K, 1.f, fj.side());
+            skinny_down(X, N, K, K, t.pdown2, K, r, 1.f, t.Hf, t.ext_b, s, t.part2, ctx.sm_count, fj.side());
+        } else {
+            cast_pad(H, r, 1, t.ext_b, EXT, N, r, EXT, s, fj.side());
+        }
+        skinny_grad(dY, N, M, M, t.ext_b, r, 1.f, dB, 1, accumulate, t.part2, ctx.sm_count, fj.side());
+    }
+    // main: dH = s * dY . B^T from the bf16 dY; extension operand dH / s_dy[n] (the reduce waits for s_dy)
+    cast_pad(B, M, 1, t.pdown, M, r, (int)M, (int)M, 1.f, st);
+    skinny_down(dY, N, M, M, t.pdown, M, r, s, t.dHf, t.ext_a, 1.f, t.part, ctx.sm_count, st, dX ? t.srow : nullptr,
+                dX ? &fj : nullptr);
+    if (dX) {
+        fj.wait(0);
+        Operand a0{t.q8, false, M}, b0{wt, false, M};
         Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
         main_gemm_f8(a0, b0, M, &a1, &b1, EXT, (__nv_bfloat16*)dX, K, N, K, nullptr, sc, ctx.sm_count, st);
     }
@@ -1078,15 +1201,7 @@ void lq_w8a8_bwd(const lq_weight* w, const void* dY, const void* X, const float*
         }
         skinny_grad(X, N, K, K, dh_plain, r, 1.f, dA, 0, accumulate, t.part, ctx.sm_count, st);
     }
-    if (dB) {
-        if (!H) {
-            cast_pad(A, 1, r, t.pdown, K, r, (int)K, (int)K, 1.f, st);
-            skinny_down(X, N, K, K, t.pdown, K, r, 1.f, t.Hf, t.ext_b, s, t.part, ctx.sm_count, st);
-        } else {
-            cast_pad(H, r, 1, t.ext_b, EXT, N, r, EXT, s, st);
-        }
-        skinny_grad(dY, N, M, M, t.ext_b, r, 1.f, dB, 1, accumulate, t.part, ctx.sm_count, st);
-    }
+    fj.join(1);
 }
 
 void lq_tc_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, int64_t ldb, void* Cout,
