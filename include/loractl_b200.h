@@ -102,6 +102,15 @@ int lq_dequant_chunk_rows(uint64_t d_out, uint64_t d_in, uint64_t chunk_bytes,
 int lq_quantize(const void* w, int w_dtype, int64_t d_out, int64_t d_in, int group, int bits,
                 void* stream, lq_weight_t** out);
 
+/* The streaming requantisation of crates/loractl-core/src/diffusion_trainer.rs:1130-1175 for a
+ * scaled-fp8 checkpoint tensor, in one pass on the device: element = LUT[byte] * weight_scale
+ * (crates/loractl-core/src/fp8.rs:305-317; `scale` scalar or per-out-channel, device pointer),
+ * then quantized like lq_quantize (crates/loractl-core/src/quant.rs:74-82).  Bit-identical to
+ * dequantizing to f32 first; the f32 tensor is never materialised.  `bytes`: device, row-major
+ * [d_out, d_in] e4m3fn. */
+int lq_quantize_from_fp8(const uint8_t* bytes, const float* scale, int scale_kind, int64_t d_out,
+                         int64_t d_in, int group, int bits, void* stream, lq_weight_t** out);
+
 /* Builds a handle from already-quantized logical data: `codes` int8 [M, K] and
  * `scales` f32 [M, K/group] on the device (the logical content of a burn QFloat
  * tensor; used to join row chunks — crates/loractl-core/src/quant.rs:130-150 — and
@@ -210,6 +219,13 @@ int lq_adamw_step(float* params, const float* grads, float* exp_avg, float* exp_
  * (crates/loractl-core/src/config.rs:503-512); a trainer calls it where the reference
  * reads the loss back (crates/loractl-core/src/diffusion_trainer.rs:1675). */
 int lq_check_device_status(void* stream);
+
+/* Self-test of that mechanism (no reference counterpart; the reference has no device-side waits):
+ * launches one warp that waits, with the kernels' own bounded-wait routine and a limit of
+ * `limit_ms` (1..1000), on a barrier nothing arrives on.  The wait runs out, the kernel records
+ * wait site 90 and returns; the next lq_check_device_status() reports LQ_ERR_TIMEOUT and clears
+ * the word, and the context stays usable.  Nothing faults or spins without a limit. */
+int lq_selftest_bounded_wait(unsigned limit_ms, void* stream);
 
 /* Launch accounting for benchmarks — the counterpart of the reference's bench probes
  * (crates/loractl-core/src/probe.rs:24-39 phase markers; crates/loractl-bench/src/lib.rs).

@@ -43,6 +43,7 @@ SIGNATURES = {
     "lq_quantize": (_I, [_P, _I, _I64, _I64, _I, _I, _P, C.POINTER(_P)]),
     "lq_weight_from_codes": (_I, [_P, _P, _I64, _I64, _I, _I, _P, C.POINTER(_P)]),
     "lq_weight_from_fp8": (_I, [_P, _P, _I, _I64, _I64, _P, C.POINTER(_P)]),
+    "lq_quantize_from_fp8": (_I, [_P, _P, _I, _I64, _I64, _I, _I, _P, C.POINTER(_P)]),
     "lq_fp8_quantize": (_I, [_P, _I64, _I64, _I, _P, C.POINTER(_P)]),
     "lq_weight_set_bias": (_I, [_P, _P, _P]),
     "lq_weight_info_get": (_I, [_P, C.POINTER(WeightInfo)]),
@@ -56,6 +57,7 @@ SIGNATURES = {
     "lq_grad_nonfinite_flag": (_I, [_P, _I64, _P, _P]),
     "lq_adamw_step": (_I, [_P, _P, _P, _P, _I64, _F, _F, _F, _F, _F, _I64, _F, _P, _P]),
     "lq_check_device_status": (_I, [_P]),
+    "lq_selftest_bounded_wait": (_I, [C.c_uint, _P]),
     "lq_kernel_launch_count": (C.c_uint64, []),
     "lq_profile_enable": (_I, [_I]),
     "lq_profile_kinds": (_I, []),

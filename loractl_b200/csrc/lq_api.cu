@@ -253,6 +253,26 @@ int lq_quantize(const void* w, int w_dtype, int64_t d_out, int64_t d_in, int gro
     });
 }
 
+int lq_quantize_from_fp8(const uint8_t* bytes, const float* scale, int scale_kind, int64_t d_out, int64_t d_in, int group,
+                         int bits, void* stream, lq_weight_t** out) {
+    return guarded([&] {
+        LQ_CHECK_ARG(out != nullptr, "out is NULL");
+        *out = nullptr;
+        LQ_CHECK_ARG(bytes != nullptr && scale != nullptr, "fp8 bytes / weight_scale pointer is NULL");
+        LQ_CHECK_ARG(scale_kind == LQ_SCALE_SCALAR || scale_kind == LQ_SCALE_PER_CHANNEL,
+                     "weight_scale must be scalar ([] or [1]) or per-out-channel ([out_features])");
+        check_int_scheme(d_out, d_in, group, bits);
+        auto h = new_handle(bits == 4 ? LQ_INT4 : LQ_INT8, d_out, d_in, group, LQ_SCALE_SCALAR);
+        try {
+            lq_launch_quantize_fp8(bytes, scale, scale_kind == LQ_SCALE_PER_CHANNEL, h.get(), bits, (cudaStream_t)stream);
+        } catch (...) {
+            free_handle(h.release());
+            throw;
+        }
+        *out = h.release();
+    });
+}
+
 int lq_weight_from_codes(const int8_t* codes, const float* scales, int64_t d_out, int64_t d_in, int group, int bits,
                          void* stream, lq_weight_t** out) {
     return guarded([&] {
@@ -473,6 +493,16 @@ int lq_check_device_status(void* stream) {
         if (code != 0)
             throw LqError(LQ_ERR_TIMEOUT, "a kernel's bounded wait gave up (wait site " + std::to_string(code) +
                                               "); its outputs are invalid");
+    });
+}
+
+int lq_selftest_bounded_wait(unsigned limit_ms, void* stream) {
+    return guarded([&] {
+        LQ_CHECK_ARG(limit_ms >= 1 && limit_ms <= 1000, "limit_ms must be in [1, 1000]");
+        int dev = 0;
+        LQ_CUDA(cudaGetDevice(&dev));
+        check_sm100(dev);
+        lq_tc_selftest_wait(dev, limit_ms, (cudaStream_t)stream);
     });
 }
 

@@ -135,6 +135,8 @@ __device__ __forceinline__ float lq_dequant_elem(const LqWView& w, int64_t m, in
 // ---- kernel launchers (defined in the .cu files) ---------------------------------
 
 void lq_launch_quantize(const void* w, int w_dtype, const lq_weight* dst, int bits, cudaStream_t st);
+void lq_launch_quantize_fp8(const uint8_t* bytes, const float* scale, int per_channel, const lq_weight* dst, int bits,
+                            cudaStream_t st);
 void lq_launch_pack_codes(const int8_t* codes, const float* scales, const lq_weight* dst, cudaStream_t st);
 void lq_launch_unpack(const lq_weight* w, int8_t* codes, float* scales, cudaStream_t st);
 // out[m * ld + k] (transpose = 0) or out[k * ld + m] (transpose = 1), dtype f32/bf16.

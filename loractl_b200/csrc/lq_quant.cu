@@ -15,6 +15,33 @@ namespace {
 __device__ __forceinline__ float ld_as_f32(const float* p, int64_t i) { return p[i]; }
 __device__ __forceinline__ float ld_as_f32(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
 
+// A scaled-fp8 weight as the quantizer's source: element (row, k) is LUT[byte] * scale in f32,
+// exactly the value crates/loractl-core/src/fp8.rs:305-317 would have written to the f32 tensor
+// that the reference then hands to quantize_linear_weight (diffusion_trainer.rs:1130-1175).
+struct Fp8Src {
+    const uint8_t* bytes;
+    const float* scale;
+    int per_channel;
+};
+
+// Two adjacent source elements (k0 even) of one row.
+__device__ __forceinline__ void ld_pair(const float* p, int64_t row, int64_t K, int64_t k0, float& v0, float& v1) {
+    const float2 v = *(const float2*)(p + row * K + k0);
+    v0 = v.x;
+    v1 = v.y;
+}
+__device__ __forceinline__ void ld_pair(const __nv_bfloat16* p, int64_t row, int64_t K, int64_t k0, float& v0, float& v1) {
+    const __nv_bfloat162 v = *(const __nv_bfloat162*)(p + row * K + k0);
+    v0 = __bfloat162float(v.x);
+    v1 = __bfloat162float(v.y);
+}
+__device__ __forceinline__ void ld_pair(const Fp8Src& s, int64_t row, int64_t K, int64_t k0, float& v0, float& v1) {
+    const uint16_t b = *(const uint16_t*)(s.bytes + row * K + k0);
+    const float sc = s.per_channel ? s.scale[row] : s.scale[0];
+    v0 = lq_decode_e4m3fn(b & 0xffu) * sc;
+    v1 = lq_decode_e4m3fn(b >> 8) * sc;
+}
+
 __device__ __forceinline__ int quant_one(float v, float scale, float qmax) {
     if (!(scale > 0.f)) return 0;
     float r = roundf(__fdiv_rn(v, scale));  // roundf: ties away from zero (Rust f32::round)
@@ -23,8 +50,8 @@ __device__ __forceinline__ int quant_one(float v, float scale, float qmax) {
 }
 
 // One warp per (padded row, k-tile): lane owns k = kt*64 + 2*lane, +1.
-template <typename T>
-__global__ void __launch_bounds__(256) quantize_kernel(const T* __restrict__ w, int64_t M, int64_t K, int G,
+template <typename Src>
+__global__ void __launch_bounds__(256) quantize_kernel(const Src w, int64_t M, int64_t K, int G,
                                                        int bits, int64_t m_tiles, int64_t k_tiles,
                                                        int64_t n_groups, void* __restrict__ packed,
                                                        float* __restrict__ scales) {
@@ -35,10 +62,7 @@ __global__ void __launch_bounds__(256) quantize_kernel(const T* __restrict__ w, 
     int64_t row = warp / k_tiles, kt = warp % k_tiles;
     int64_t k0 = kt * LQ_TILE_K + 2 * lane;
     float v0 = 0.f, v1 = 0.f;
-    if (row < M && k0 < K) {  // K is even, so k0 + 1 < K too
-        v0 = ld_as_f32(w, row * K + k0);
-        v1 = ld_as_f32(w, row * K + k0 + 1);
-    }
+    if (row < M && k0 < K) ld_pair(w, row, K, k0, v0, v1);  // K is even, so k0 + 1 < K too
     float a = fmaxf(fabsf(v0), fabsf(v1));
     int span = G / 2;  // lanes per group: 16 (G = 32) or 32 (G = 64)
     for (int off = span / 2; off >= 1; off >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, off));
@@ -330,12 +354,22 @@ void lq_launch_quantize(const void* w, int w_dtype, const lq_weight* d, int bits
     int64_t warps = d->m_tiles * LQ_TILE_M * d->k_tiles;
     unsigned grid = blocks_for(warps, 8);
     if (w_dtype == LQ_F32)
-        quantize_kernel<float><<<grid, 256, 0, st>>>((const float*)w, d->M, d->K, d->group, bits, d->m_tiles,
-                                                     d->k_tiles, d->n_groups, d->packed, d->scales);
+        quantize_kernel<const float*><<<grid, 256, 0, st>>>((const float*)w, d->M, d->K, d->group, bits, d->m_tiles,
+                                                            d->k_tiles, d->n_groups, d->packed, d->scales);
     else
-        quantize_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)w, d->M, d->K, d->group, bits,
-                                                             d->m_tiles, d->k_tiles, d->n_groups, d->packed,
-                                                             d->scales);
+        quantize_kernel<const __nv_bfloat16*><<<grid, 256, 0, st>>>((const __nv_bfloat16*)w, d->M, d->K, d->group,
+                                                                    bits, d->m_tiles, d->k_tiles, d->n_groups,
+                                                                    d->packed, d->scales);
+    LQ_CUDA(cudaGetLastError());
+}
+
+void lq_launch_quantize_fp8(const uint8_t* bytes, const float* scale, int per_channel, const lq_weight* d, int bits,
+                            cudaStream_t st) {
+    LqProf prof(LQ_K_QUANT, st);
+    int64_t warps = d->m_tiles * LQ_TILE_M * d->k_tiles;
+    Fp8Src src{bytes, scale, per_channel};
+    quantize_kernel<Fp8Src><<<blocks_for(warps, 8), 256, 0, st>>>(src, d->M, d->K, d->group, bits, d->m_tiles,
+                                                                  d->k_tiles, d->n_groups, d->packed, d->scales);
     LQ_CUDA(cudaGetLastError());
 }
 

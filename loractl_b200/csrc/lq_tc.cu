@@ -1204,6 +1204,31 @@ void lq_w8a8_bwd(const lq_weight* w, const void* dY, const void* X, const float*
     fj.join(1);
 }
 
+// ---- self-test of the bounded wait ----------------------------------------------------------
+// One warp waits on an mbarrier that nothing ever arrives on, with the same wait routine the GEMM
+// kernels use but a caller-chosen limit.  The wait gives up after the limit, records `code` in the
+// per-device error word and the kernel returns normally: the context stays usable and the host
+// sees LQ_ERR_TIMEOUT from lq_check_device_status.  Nothing here faults, traps or spins unbounded.
+namespace {
+__global__ void selftest_wait_kernel(int* status, unsigned long long limit_ns, int code) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    mbar_wait_ns(smem_u32(&bar), 0, &abort_flag, status, code, limit_ns);
+}
+}  // namespace
+
+void lq_tc_selftest_wait(int device, unsigned limit_ms, cudaStream_t st) {
+    DevCtx& ctx = dev_ctx(device);
+    selftest_wait_kernel<<<1, 32, 0, st>>>(ctx.status, (unsigned long long)limit_ms * 1000000ull, 90);
+    LQ_CUDA(cudaGetLastError());
+}
+
 void lq_tc_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, int64_t ldb, void* Cout,
                      int c_dtype, int64_t ldc, int64_t Mg, int64_t Ng, int64_t Kg, int block_n, int splits,
                      float* partial_ws, const float* bias, cudaStream_t st) {

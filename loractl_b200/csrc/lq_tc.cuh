@@ -25,6 +25,9 @@ void lq_tc_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B, int b_
 // Per-device error word written by kernels whose bounded waits gave up.  Synchronises `st`.
 int lq_tc_read_status(int device, cudaStream_t st);
 
+// Launches a one-warp kernel whose bounded wait is certain to run out after `limit_ms` (wait site 90).
+void lq_tc_selftest_wait(int device, unsigned limit_ms, cudaStream_t st);
+
 // Shared with the fused small-batch kernel (lq_fused.cu).
 // 2-D bf16 tensor map over [rows, inner] (ld elements between rows), box 64 x box_rows, 128-byte swizzle.
 CUtensorMap lq_tc_make_map(const void* base, int64_t inner, int64_t rows, int64_t ld, int box_rows);

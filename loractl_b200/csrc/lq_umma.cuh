@@ -45,21 +45,25 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // already aborted); the caller must then leave its loop.  `abort_flag` lives in shared
 // memory; `status` is the per-device error word in global memory.
 #define LQ_WAIT_LIMIT_NS 2000000000ull
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int code) {
+__device__ __forceinline__ bool mbar_wait_ns(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                             int code, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = globaltimer_ns();
     for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255u) == 0u) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > LQ_WAIT_LIMIT_NS) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 return false;
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                          int code) {
+    return mbar_wait_ns(bar, parity, abort_flag, status, code, LQ_WAIT_LIMIT_NS);
 }
 
 // ---- TMA ------------------------------------------------------------------------
