@@ -89,6 +89,105 @@ __global__ void __launch_bounds__(256) quantize_kernel(const Src w, int64_t M, i
     }
 }
 
+// Sixteen adjacent source elements (k0 a multiple of 16) of one row, as f32.
+__device__ __forceinline__ void ld16(const float* p, int64_t row, int64_t K, int64_t k0, float (&v)[16]) {
+    const float4* s = (const float4*)(p + row * K + k0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 f = s[i];
+        v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+    }
+}
+__device__ __forceinline__ void ld16(const __nv_bfloat16* p, int64_t row, int64_t K, int64_t k0, float (&v)[16]) {
+    const uint4* s = (const uint4*)(p + row * K + k0);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const uint4 u = s[i];
+        const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            v[8 * i + 2 * j] = __uint_as_float(w4[j] << 16);
+            v[8 * i + 2 * j + 1] = __uint_as_float(w4[j] & 0xFFFF0000u);
+        }
+    }
+}
+// e4m3 -> f16 is exact for every code (hardware conversion), f16 -> f32 is exact, so this is
+// LUT[byte] * scale bit for bit.
+__device__ __forceinline__ void ld16(const Fp8Src& s, int64_t row, int64_t K, int64_t k0, float (&v)[16]) {
+    const uint4 u = *(const uint4*)(s.bytes + row * K + k0);
+    const float sc = s.per_channel ? s.scale[row] : s.scale[0];
+    const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)((w4[j] >> (16 * h)) & 0xFFFFu), __NV_E4M3);
+            const float2 f = __half22float2(*(const __half2*)&hr);
+            v[4 * j + 2 * h] = f.x * sc;
+            v[4 * j + 2 * h + 1] = f.y * sc;
+        }
+    }
+}
+
+// The load-time quantizer at HBM speed.  One warp per (8 consecutive rows, k-tile); lane =
+// (row i = lane >> 2, quarter q = lane & 3) owns the 16 elements k = kt*64 + 16q .. +15: a
+// 16/32/64-byte vector load per lane, 64 B per row and 8 rows per warp fully used; group absmax by
+// one or two shuffles; the lane writes its two packed words (int4) or 16 bytes (int8), so a warp
+// stores 256 (512) contiguous bytes of the tile and 8 consecutive scales.  Needs a 16-byte-aligned
+// source and K % 16 == 0 (true whenever K % block == 0).
+template <typename Src>
+__global__ void __launch_bounds__(256) quantize16_kernel(const Src w, int64_t M, int64_t K, int G, int bits,
+                                                         int64_t m_tiles, int64_t k_tiles, int64_t n_groups,
+                                                         void* __restrict__ packed, float* __restrict__ scales) {
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= m_tiles * 16 * k_tiles) return;
+    const int64_t unit = warp / k_tiles, kt = warp % k_tiles;
+    const int64_t row = unit * 8 + (lane >> 2);
+    const int q = lane & 3;
+    const int64_t k0 = kt * LQ_TILE_K + 16 * q;
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+    if (row < M && k0 < K) ld16(w, row, K, k0, v);
+    float a = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) a = fmaxf(a, fabsf(v[i]));
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+    if (G == 64) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
+    const float qmax = bits == 4 ? 7.f : 127.f;
+    const float scale = __fdiv_rn(a, qmax);
+    const int64_t mt = row >> 7, r = row & 127;
+    const int64_t g = k0 / G;
+    if (g < n_groups && (G == 64 ? q == 0 : (q & 1) == 0)) scales[(mt * n_groups + g) * 128 + r] = scale;
+    if (bits == 4) {
+        uint32_t word[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t acc = 0;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const uint32_t u = (uint32_t)(quant_one(v[8 * h + e], scale, qmax) + 8);
+                acc |= u << (4 * ((e >> 1) + 4 * (e & 1)));
+            }
+            word[h] = acc;
+        }
+        uint32_t* tile = (uint32_t*)packed + (mt * k_tiles + kt) * 1024;
+        *(uint2*)(tile + r * 8 + 2 * q) = make_uint2(word[0], word[1]);
+    } else {
+        uint32_t word[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t acc = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc |= ((uint32_t)quant_one(v[4 * j + e], scale, qmax) & 0xffu) << (8 * e);
+            word[j] = acc;
+        }
+        uint8_t* tile = (uint8_t*)packed + (mt * k_tiles + kt) * 8192;
+        *(uint4*)(tile + r * 64 + 16 * q) = make_uint4(word[0], word[1], word[2], word[3]);
+    }
+}
+
 // Same tiling, from logical codes [M,K] + scales [M,K/G].
 __global__ void __launch_bounds__(256) pack_codes_kernel(const int8_t* __restrict__ codes,
                                                          const float* __restrict__ sc_in, int64_t M, int64_t K,
@@ -349,28 +448,31 @@ inline unsigned blocks_for(int64_t n, int per) { return (unsigned)((n + per - 1)
 
 }  // namespace
 
+template <typename Src>
+static void launch_quantize_src(const Src& src, const void* base, const lq_weight* d, int bits, cudaStream_t st) {
+    if (((uintptr_t)base & 15) == 0 && d->K % 16 == 0) {
+        const int64_t warps = d->m_tiles * 16 * d->k_tiles;
+        quantize16_kernel<Src><<<blocks_for(warps, 8), 256, 0, st>>>(src, d->M, d->K, d->group, bits, d->m_tiles, d->k_tiles,
+                                                                    d->n_groups, d->packed, d->scales);
+    } else {  // unaligned source: the element-pair kernel
+        const int64_t warps = d->m_tiles * LQ_TILE_M * d->k_tiles;
+        quantize_kernel<Src><<<blocks_for(warps, 8), 256, 0, st>>>(src, d->M, d->K, d->group, bits, d->m_tiles, d->k_tiles,
+                                                                  d->n_groups, d->packed, d->scales);
+    }
+    LQ_CUDA(cudaGetLastError());
+}
+
 void lq_launch_quantize(const void* w, int w_dtype, const lq_weight* d, int bits, cudaStream_t st) {
     LqProf prof(LQ_K_QUANT, st);
-    int64_t warps = d->m_tiles * LQ_TILE_M * d->k_tiles;
-    unsigned grid = blocks_for(warps, 8);
-    if (w_dtype == LQ_F32)
-        quantize_kernel<const float*><<<grid, 256, 0, st>>>((const float*)w, d->M, d->K, d->group, bits, d->m_tiles,
-                                                            d->k_tiles, d->n_groups, d->packed, d->scales);
-    else
-        quantize_kernel<const __nv_bfloat16*><<<grid, 256, 0, st>>>((const __nv_bfloat16*)w, d->M, d->K, d->group,
-                                                                    bits, d->m_tiles, d->k_tiles, d->n_groups,
-                                                                    d->packed, d->scales);
-    LQ_CUDA(cudaGetLastError());
+    if (w_dtype == LQ_F32) launch_quantize_src<const float*>((const float*)w, w, d, bits, st);
+    else launch_quantize_src<const __nv_bfloat16*>((const __nv_bfloat16*)w, w, d, bits, st);
 }
 
 void lq_launch_quantize_fp8(const uint8_t* bytes, const float* scale, int per_channel, const lq_weight* d, int bits,
                             cudaStream_t st) {
     LqProf prof(LQ_K_QUANT, st);
-    int64_t warps = d->m_tiles * LQ_TILE_M * d->k_tiles;
     Fp8Src src{bytes, scale, per_channel};
-    quantize_kernel<Fp8Src><<<blocks_for(warps, 8), 256, 0, st>>>(src, d->M, d->K, d->group, bits, d->m_tiles,
-                                                                  d->k_tiles, d->n_groups, d->packed, d->scales);
-    LQ_CUDA(cudaGetLastError());
+    launch_quantize_src<Fp8Src>(src, bytes, d, bits, st);
 }
 
 void lq_launch_pack_codes(const int8_t* codes, const float* scales, const lq_weight* d, cudaStream_t st) {

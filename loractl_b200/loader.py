@@ -21,6 +21,8 @@ from __future__ import annotations
 
 import ctypes as C
 import json
+import os
+from concurrent.futures import ThreadPoolExecutor
 import mmap
 import struct
 from dataclasses import dataclass
@@ -78,6 +80,12 @@ class SafetensorsFile:
             if e < b or self._data0 + e > len(self._mm) or (want is not None and want != e - b):
                 raise CheckpointError(f"'{name}' has inconsistent data offsets [{b}, {e}) in {self.path}")
             self.entries[name] = ent
+
+    def fileno(self) -> int:
+        return self._f.fileno()
+
+    def file_offset(self, name: str) -> int:
+        return self._data0 + self.entries[name].begin
 
     def raw(self, name: str) -> memoryview:
         ent = self.entries[name]
@@ -191,6 +199,32 @@ class LoadReport:
     packed_bytes: int = 0      # bytes of packed weights + scales now resident
 
 
+_COPY_THREADS = 8
+
+
+def _host_read(fd: int, dst: np.ndarray, offset: int, pool: ThreadPoolExecutor) -> None:
+    """Reads one tensor's bytes from the file straight into pinned memory with positional reads,
+    split over a few threads for large tensors (the read releases the GIL).  Reading, unlike copying
+    out of a fresh mapping, takes no page fault per 4 KB of checkpoint."""
+    n = dst.shape[0]
+
+    def read(o: int, m: int) -> None:
+        done = 0
+        while done < m:
+            got = os.preadv(fd, [memoryview(dst[o + done:o + m])], offset + o + done)
+            if got <= 0:
+                raise CheckpointError("unexpected end of checkpoint file")
+            done += got
+
+    if n < (8 << 20):
+        read(0, n)
+        return
+    step = ((-(-n // _COPY_THREADS)) + 4095) & ~4095
+    futs = [pool.submit(read, o, min(step, n - o)) for o in range(0, n, step)]
+    for f in futs:
+        f.result()
+
+
 class _Slot:
     def __init__(self, nbytes: int, device: torch.device):
         self.host = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
@@ -198,6 +232,26 @@ class _Slot:
         self.uploaded = torch.cuda.Event()
         self.consumed = torch.cuda.Event()
         self.used = False
+
+
+_STAGING: Dict[torch.device, List[_Slot]] = {}
+
+
+def _staging(device: torch.device, nbytes: int) -> List[_Slot]:
+    """The two staging slots of a device, kept between calls (pinning host memory costs more than
+    uploading through it) and grown when a checkpoint holds a larger tensor."""
+    cur = _STAGING.get(device)
+    if cur is None or cur[0].host.numel() < nbytes:
+        cur = [_Slot(nbytes, device), _Slot(nbytes, device)]
+        _STAGING[device] = cur
+    for sl in cur:
+        sl.used = False
+    return cur
+
+
+def release_staging() -> None:
+    """Frees the pinned and device staging buffers kept by `load_quant_module`."""
+    _STAGING.clear()
 
 
 def load_quant_module(path: str, device: torch.device, bits: int = 4, block: int = 64,
@@ -214,16 +268,27 @@ def load_quant_module(path: str, device: torch.device, bits: int = 4, block: int
     if bits not in (4, 8):
         raise ValueError("bits must be 4 or 8")
     device = torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
     lib = L.lib()
     handles: Dict[str, QuantWeight] = {}
     plain: Dict[str, torch.Tensor] = {}
     rep = LoadReport()
     with SafetensorsFile(path) as sf, torch.cuda.device(device):
         plan = classify(sf)
-        nmax = max((sf.entries[p.name].end - sf.entries[p.name].begin for p in plan), default=0)
+        def slot_bytes(p: PlanItem) -> int:
+            e = sf.entries[p.name]
+            extra = 0
+            if p.scale_name:  # the sidecar rides in the same slot, after the weight bytes
+                se = sf.entries[p.scale_name]
+                extra = 256 + (se.end - se.begin)
+            return ((e.end - e.begin + 255) & ~255) + extra
+
+        nmax = max((slot_bytes(p) for p in plan), default=0)
         if nmax == 0:
             return handles, plain, rep
-        slots = [_Slot(nmax, device), _Slot(nmax, device)]
+        slots = _staging(device, nmax)
+        pool = ThreadPoolExecutor(max_workers=_COPY_THREADS)
         copy_stream = torch.cuda.Stream(device)
         main = torch.cuda.current_stream(device)
         sp = _stream_ptr(device)
@@ -235,10 +300,18 @@ def load_quant_module(path: str, device: torch.device, bits: int = 4, block: int
             slot = slots[i & 1]
             if slot.used:
                 slot.consumed.synchronize()  # the kernel that read this slot's device buffer is done
-            # host: file pages -> pinned staging (the only host-side touch of the data)
-            np.copyto(slot.host.numpy()[:n], np.frombuffer(sf.raw(item.name), dtype=np.uint8))
+            # host: checkpoint bytes -> pinned staging (the only host-side touch of the data); the
+            # fp8 sidecar follows the weight in the same slot so that one upload carries both
+            hostv = slot.host.numpy()
+            _host_read(sf.fileno(), hostv[:n], sf.file_offset(item.name), pool)
+            total, s_off, s_n = n, 0, 0
+            if item.scale_name:
+                se = sf.entries[item.scale_name]
+                s_off, s_n = (n + 255) & ~255, se.end - se.begin
+                _host_read(sf.fileno(), hostv[s_off:s_off + s_n], sf.file_offset(item.scale_name), pool)
+                total = s_off + s_n
             with torch.cuda.stream(copy_stream):
-                slot.dev[:n].copy_(slot.host[:n], non_blocking=True)
+                slot.dev[:total].copy_(slot.host[:total], non_blocking=True)
                 slot.uploaded.record(copy_stream)
             main.wait_event(slot.uploaded)
             slot.used = True
@@ -247,8 +320,8 @@ def load_quant_module(path: str, device: torch.device, bits: int = 4, block: int
                            and item.shape[1] > 0 and (want is None or want(item.name, item.shape)))
             src = slot.dev[:n]
             if item.dtype == "F8_E4M3":
-                sc = torch.frombuffer(bytearray(sf.raw(item.scale_name)), dtype=torch.float32).reshape(-1).to(device)
-                rep.file_bytes += sc.numel() * 4
+                sc = slot.dev[s_off:s_off + s_n].view(torch.float32)
+                rep.file_bytes += s_n
                 if len(item.shape) != 2:
                     raise CheckpointError(f"fp8 tensor '{item.name}' is not 2-D in {sf.path}")
                 out = C.c_void_p()
@@ -270,7 +343,6 @@ def load_quant_module(path: str, device: torch.device, bits: int = 4, block: int
                     main.synchronize()
                     del tmp
                     rep.left_plain += 1
-                sc.record_stream(main)
             else:
                 t = src.view(_TORCH_DTYPE[item.dtype]).reshape(item.shape)
                 if quantizable and item.dtype in ("F32", "BF16"):
@@ -292,6 +364,7 @@ def load_quant_module(path: str, device: torch.device, bits: int = 4, block: int
                     rep.left_plain += 1
             slot.consumed.record(main)
         main.synchronize()
+        pool.shutdown()
         if progress:
             progress("", len(plan), len(plan))
     for h in handles.values():
