@@ -44,9 +44,9 @@ WORKLOADS = {
 }
 METRIC = "LoRA-linear fwd+bwd TFLOP/s"
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of the dominant kernel, from
-# the ncu capture summarised in profiles/umma_gemm_cfg2_step.md: forward 528.3 MB, backward
-# 872.5 MB, averaged like `achieved` is over the two launches of a step.
-NCU_TRAFFIC_BYTES = {"cfg2": (528.35e6 + 872.54e6) / 2}
+# the ncu capture summarised in profiles/umma_gemm_cfg2_step.md: forward 534.2 MB, backward
+# 874.0 MB, averaged like `achieved` is over the two launches of a step.
+NCU_TRAFFIC_BYTES = {"cfg2": (534.23e6 + 873.95e6) / 2}
 
 
 def step_flops(n, k, m, r):
