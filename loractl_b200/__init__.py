@@ -13,7 +13,9 @@ from .fp8 import e4m3fn_lut, fp8_quantize, weight_from_fp8
 from .config import BackendKind, ComputeConfig, Precision, validate_b200
 from .optim import AdamW, DynamicLossScale, FlatAdapters, nonfinite_flag
 from .block_ckpt import checkpointed_step
-from . import dp
+from . import dp, export, loader
+from .export import export_adapters, import_adapters
+from .loader import load_quant_module
 
 __all__ = [
     "QUANT_BLOCK", "Quant", "QuantWeight", "check_device_status", "dequant_chunk_rows", "quant_matmul_t",
@@ -22,4 +24,5 @@ __all__ = [
     "build_adapters", "BaseLinear", "QuantLinear", "site", "e4m3fn_lut", "fp8_quantize", "weight_from_fp8",
     "BackendKind", "ComputeConfig", "Precision", "validate_b200",
     "AdamW", "DynamicLossScale", "FlatAdapters", "nonfinite_flag", "checkpointed_step", "dp",
+    "export", "loader", "export_adapters", "import_adapters", "load_quant_module",
 ]

@@ -9,7 +9,8 @@ It writes two kinds of fixtures, all small JSON:
 1. Pass-through copies of the vectors the reference's own tests pin for this
    path (crates/loractl-core/tests/fixtures/quant_int4_golden.json,
    quant_int8_golden.json, fp8_lut_golden.json, fp8_dequant_golden.json and
-   crates/loractl-core/tests/golden/lora_toy.json), re-emitted unchanged, plus the
+   crates/loractl-core/tests/golden/lora_toy.json, lora_export.json,
+   krea2_lora_keys.json), re-emitted unchanged, plus the
    fixed constants of reference/lora_reference.py:39-66 (W_BASE, A_INIT, X, T)
    that the toy replays.
 2. Extra vectors produced by *importing the reference's Python generators*
@@ -42,6 +43,8 @@ def passthrough(ref: pathlib.Path) -> None:
         "fixtures/fp8_lut_golden.json",
         "fixtures/fp8_dequant_golden.json",
         "golden/lora_toy.json",
+        "golden/lora_export.json",
+        "golden/krea2_lora_keys.json",
     ):
         data = json.loads((core / rel).read_text())
         (HERE / pathlib.Path(rel).name).write_text(json.dumps(data))
