@@ -210,6 +210,31 @@ int lq_adamw_step(float* params, const float* grads, float* exp_avg, float* exp_
                   float lr, float beta1, float beta2, float eps, float weight_decay, int64_t step,
                   float grad_scale, const int* skip_flag, void* stream);
 
+/* ---- element-wise companions of the linears inside a DiT block ------------------ */
+
+/* crates/loractl-core/src/mmdit.rs:857-869: the block's `(scale + 1) * norm(x) + shift` prologues
+ * and `x + gate * f(..)` residuals, which the reference runs as separate broadcast multiplies and
+ * adds.  x, y, out: [samples, tokens, h] contiguous; shift, scale, gate: [samples, h] contiguous,
+ * broadcast over the tokens of their sample; `dtype` LQ_F32 or LQ_BF16 for all of them.  The norm is
+ * a layer norm over h without affine parameters, statistics in f32; `mean`, `rstd`: f32 [samples *
+ * tokens], written by the forward and read by the backward.  The backward's token-axis sums
+ * (`dshift`, `dscale`, `dgate`: f32 [samples, h]) are reduced in a fixed order (no atomics) through
+ * `ws`, at least lq_block_ops_workspace_bytes() bytes. */
+size_t lq_block_ops_workspace_bytes(int64_t samples, int64_t tokens, int64_t h);
+int lq_ln_modulate_fwd(const void* x, const void* shift, const void* scale, int dtype, int64_t samples,
+                       int64_t tokens, int64_t h, float eps, void* y, float* mean, float* rstd,
+                       void* stream);
+int lq_ln_modulate_bwd(const void* dy, const void* x, const void* scale, const float* mean,
+                       const float* rstd, int dtype, int64_t samples, int64_t tokens, int64_t h,
+                       void* dx, float* dshift, float* dscale, void* ws, size_t ws_bytes, void* stream);
+/* out = x + gate * y. */
+int lq_gate_residual_fwd(const void* x, const void* gate, const void* y, int dtype, int64_t samples,
+                         int64_t tokens, int64_t h, void* out, void* stream);
+/* dy = gate * dout, dgate = sum over tokens of dout * y (d x is dout itself). */
+int lq_gate_residual_bwd(const void* dout, const void* gate, const void* y, int dtype, int64_t samples,
+                         int64_t tokens, int64_t h, void* dy, float* dgate, void* ws, size_t ws_bytes,
+                         void* stream);
+
 /* ---- diagnostics -------------------------------------------------------------- */
 
 /* Device-side waits in the kernels are bounded; one that gives up records a code in a

@@ -14,7 +14,7 @@ import sys
 PKG = pathlib.Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "lib" / "libloractl_b200.so"
-SOURCES = ["lq_api.cu", "lq_quant.cu", "lq_simt.cu", "lq_tc.cu", "lq_prof.cu", "lq_step.cu", "lq_fused.cu"]
+SOURCES = ["lq_api.cu", "lq_quant.cu", "lq_simt.cu", "lq_tc.cu", "lq_prof.cu", "lq_step.cu", "lq_fused.cu", "lq_block.cu"]
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",

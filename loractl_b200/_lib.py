@@ -56,6 +56,11 @@ SIGNATURES = {
     "lq_weight_prepare_fp8_backward": (_I, [_P, _P]),
     "lq_grad_nonfinite_flag": (_I, [_P, _I64, _P, _P]),
     "lq_adamw_step": (_I, [_P, _P, _P, _P, _I64, _F, _F, _F, _F, _F, _I64, _F, _P, _P]),
+    "lq_block_ops_workspace_bytes": (C.c_size_t, [_I64, _I64, _I64]),
+    "lq_ln_modulate_fwd": (_I, [_P, _P, _P, _I, _I64, _I64, _I64, C.c_float, _P, _P, _P, _P]),
+    "lq_ln_modulate_bwd": (_I, [_P, _P, _P, _P, _P, _I, _I64, _I64, _I64, _P, _P, _P, _P, C.c_size_t, _P]),
+    "lq_gate_residual_fwd": (_I, [_P, _P, _P, _I, _I64, _I64, _I64, _P, _P]),
+    "lq_gate_residual_bwd": (_I, [_P, _P, _P, _I, _I64, _I64, _I64, _P, _P, _P, C.c_size_t, _P]),
     "lq_check_device_status": (_I, [_P]),
     "lq_selftest_bounded_wait": (_I, [C.c_uint, _P]),
     "lq_kernel_launch_count": (C.c_uint64, []),

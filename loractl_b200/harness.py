@@ -8,8 +8,9 @@ per stream a joint-qkv 3072 -> 9216, out-projection 3072 -> 3072, MLP up 3072 ->
 12288 -> 3072 and an adaLN modulation 3072 -> 18432 on the conditioning vector — which is a
 synthetic composition: the reference's own denoiser is the single-stream Krea-2 DiT
 (crates/loractl-core/src/mmdit.rs:540-870), whose injectable sites this mirrors only in kind
-(`site()` at mmdit.rs:526-536 around each projection).  Attention, norms and activations are
-plain PyTorch ops (not kernels of this package); they are the callers either side of the path.
+(`site()` at mmdit.rs:526-536 around each projection).  The modulated layer norms and the gated
+residuals are this package's fused element-wise kernels (`block_ops`); attention and GELU are
+plain PyTorch ops — the callers either side of the path.
 
 The step mirrors crates/loractl-core/src/diffusion_trainer.rs:1599-1743 with
 `compute.grad_checkpointing` on: flow-matching inputs (crates/loractl-core/src/flow.rs:50-66),
@@ -28,6 +29,7 @@ from torch import nn
 from . import dp
 from .adapters import LoraAdapters, LoraConfig, LoraSite, TargetSpec, build_adapters
 from .block_ckpt import checkpointed_step
+from .block_ops import gated_residual, modulated_layer_norm
 from .linear import BaseLinear, QuantLinear, site
 from .optim import AdamW, DynamicLossScale, FlatAdapters, nonfinite_flag
 from .quant import quantize_linear_weight
@@ -88,7 +90,7 @@ class DoubleStreamBlock(nn.Module):
         for s in self.STREAMS:
             mods[s] = self._lin(s, "mod", cond).unsqueeze(1).chunk(6, dim=-1)
             shift, scale = mods[s][0], mods[s][1]
-            xn = F.layer_norm(xs[s], (h,)) * (1 + scale) + shift
+            xn = modulated_layer_norm(xs[s], shift, scale)  # LN(x) * (1 + scale) + shift, one kernel
             qkvs[s] = self._lin(s, "qkv", xn).view(b, -1, 3, cfg.heads, h // cfg.heads)
         qkv = torch.cat([qkvs["img"], qkvs["txt"]], dim=1)  # joint attention over both streams
         q, k, v = (t.transpose(1, 2) for t in qkv.unbind(2))
@@ -97,9 +99,9 @@ class DoubleStreamBlock(nn.Module):
         outs = []
         for s in self.STREAMS:
             _, _, gate1, shift2, scale2, gate2 = mods[s]
-            x = xs[s] + gate1 * self._lin(s, "out", atts[s])
-            xn = F.layer_norm(x, (h,)) * (1 + scale2) + shift2
-            x = x + gate2 * self._lin(s, "down", F.gelu(self._lin(s, "up", xn), approximate="tanh"))
+            x = gated_residual(xs[s], gate1, self._lin(s, "out", atts[s]))
+            xn = modulated_layer_norm(x, shift2, scale2)
+            x = gated_residual(x, gate2, self._lin(s, "down", F.gelu(self._lin(s, "up", xn), approximate="tanh")))
             outs.append(x)
         return torch.cat(outs, dim=1)
 
