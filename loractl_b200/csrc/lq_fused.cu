@@ -20,6 +20,8 @@
 // bf16 once per group (relative 2^-9), inside the bf16 path's stated tolerance.
 #include <algorithm>
 
+#include <cuda_fp8.h>
+
 #include "lq_prof.cuh"
 #include "lq_tc.cuh"
 #include "lq_umma.cuh"
@@ -572,6 +574,173 @@ stream_small_fwd_kernel(const __grid_constant__ CUtensorMap tmX, FusedParams p) 
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// N <= 16 tokens, scaled-fp8 weights: the same register route over the file's row-major e4m3 bytes.
+//
+// A stage is one 2-D tensor copy of [128 weight rows][128 bytes of k] (two k-tiles, 128-byte
+// swizzled) plus the matching two X tiles.  Lane (g, t) reads the 16-byte chunk t (+4 for the second
+// k-tile) of fragment rows g and g + 8: four 32-bit words = four k16 steps, each word giving the
+// pairs (b0,b1) | (b2,b3); e4m3 pairs become bf16 pairs through the hardware e4m3x2 -> f16x2
+// conversion (exact) and an f16 -> f32 -> bf16 round trip (exact as well: 3 mantissa bits).  The X
+// fragment is the 32 bytes k = 16t .. 16t+15 of a token row.  Fragment row g stands for tile row
+// (g >> 1) + 4 (g & 1) of its group of 8 so that the swizzled reads of two rows never share a bank
+// group.  The per-channel (or scalar) f32 scale multiplies the finished row sums, so no weight is
+// rounded.  Partials and the H rows are handled as in the int4 kernel.
+constexpr int KS_F8 = 2;
+constexpr uint32_t F8_W_BYTES = 128 * 128;
+constexpr uint32_t F8_RAW_BYTES = KS_F8 * STREAM_X_BYTES + F8_W_BYTES;
+constexpr int F8_STAGES = 3;
+constexpr size_t F8_SMEM = (size_t)F8_STAGES * F8_RAW_BYTES + 1024 + 128;
+
+__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint32_t two_bytes) {
+    const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(two_bytes & 0xFFFFu), __NV_E4M3);
+    const float2 f = __half22float2(*(const __half2*)&hr);
+    const __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+    return *(const uint32_t*)&b;
+}
+
+struct StreamF8Params {
+    FusedParams base;       // packed / scales / group unused
+    const float* wscale;    // [M] or [1]
+    int per_channel;
+};
+
+template <int NB>
+__global__ void __launch_bounds__(kStreamThreads, STREAM_CTAS_PER_SM)
+stream_small_fp8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, StreamF8Params q) {
+    const FusedParams& p = q.base;
+    constexpr int RS = F8_STAGES;
+    extern __shared__ uint8_t smem_raw_[];
+    uint8_t* raw = (uint8_t*)(((uintptr_t)smem_raw_ + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(raw + (size_t)RS * F8_RAW_BYTES);
+    uint64_t* full_raw = bars;
+    uint64_t* empty_raw = bars + RS;
+    volatile int* abort_flag = (volatile int*)(bars + 2 * RS);
+
+    if ((int)blockIdx.x < p.h_blocks) {  // uniform per CTA
+        stream_h_block(p, (int)blockIdx.x, (float*)raw);
+        return;
+    }
+    const int first = (int)blockIdx.x - p.h_blocks, stride = (int)gridDim.x - p.h_blocks;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < RS; ++s) {
+            mbar_init(smem_u32(&full_raw[s]), 1);
+            mbar_init(smem_u32(&empty_raw[s]), 4);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tmX);
+        prefetch_tmap(&tmW);
+    }
+    __syncthreads();
+
+    const int num_items = p.m_tiles * p.splits;
+    constexpr uint32_t W_OFF = 0, X_OFF = F8_W_BYTES;  // the weight box wants 1024-byte alignment; so do the X tiles
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int item = first; ok && item < num_items; item += stride) {
+                const int mt = item / p.splits, z = item - mt * p.splits;
+                const int kt0 = (int)(((long long)z * p.k_tiles) / p.splits) & ~1;  // splits start on a 128-byte box
+                const int kt1 = z + 1 == p.splits ? p.k_tiles : ((int)(((long long)(z + 1) * p.k_tiles) / p.splits) & ~1);
+                for (int kt = kt0; kt < kt1; kt += KS_F8) {
+                    if (!mbar_wait(smem_u32(&empty_raw[s]), phase ^ 1u, abort_flag, p.status, 33)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(&full_raw[s]);
+                    const uint32_t base = smem_u32(raw + (size_t)s * F8_RAW_BYTES);
+                    mbar_expect_tx(bar, F8_RAW_BYTES);  // both boxes are always whole (out-of-range parts are zero-filled)
+                    tma_load_2d(base + W_OFF, &tmW, bar, kt * 64, mt * 128);
+                    tma_load_3d(base + X_OFF, &tmX, bar, 0, 0, kt);
+                    if (++s == RS) { s = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok)
+                for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    const int cw = warp - 1, g = lane >> 2, t = lane & 3;
+    const int rho = (g >> 1) + 4 * (g & 1);  // tile row (within a group of 8) held by fragment row g
+    const uint32_t x_off = (uint32_t)g * 128u;  // token g of a block of 8; chunks 2t, 2t+1 swizzled by (g & 7)
+    const uint32_t xc0 = ((uint32_t)(2 * t) ^ (uint32_t)g) << 4, xc1 = ((uint32_t)(2 * t + 1) ^ (uint32_t)g) << 4;
+    int s = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int item = first; ok && item < num_items; item += stride) {
+        const int mt = item / p.splits, z = item - mt * p.splits;
+        const int kt0 = (int)(((long long)z * p.k_tiles) / p.splits) & ~1;
+        const int kt1 = z + 1 == p.splits ? p.k_tiles : ((int)(((long long)(z + 1) * p.k_tiles) / p.splits) & ~1);
+        float tot[2][NB][4];
+#pragma unroll
+        for (int mb = 0; mb < 2; ++mb)
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) tot[mb][nb][e] = 0.f;
+        for (int kt = kt0; ok && kt < kt1; kt += KS_F8) {
+            if (!mbar_wait(smem_u32(&full_raw[s]), phase, abort_flag, p.status, 34)) { ok = false; break; }
+            const uint8_t* stage = raw + (size_t)s * F8_RAW_BYTES;
+#pragma unroll
+            for (int j = 0; j < KS_F8; ++j) {
+                const uint8_t* xs = stage + X_OFF + j * STREAM_X_BYTES;
+                uint4 xa[NB], xb[NB];
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) {
+                    xa[nb] = *(const uint4*)(xs + nb * 1024 + x_off + xc0);
+                    xb[nb] = *(const uint4*)(xs + nb * 1024 + x_off + xc1);
+                }
+#pragma unroll
+                for (int mb = 0; mb < 2; ++mb) {
+                    const int r0 = cw * 32 + mb * 16 + rho;  // rows r0 and r0 + 8 of the tile; (r0 & 7) == rho
+                    const uint32_t c = ((uint32_t)(4 * j + t) ^ (uint32_t)rho) << 4;
+                    const uint4 wg = *(const uint4*)(stage + W_OFF + (uint32_t)r0 * 128u + c);
+                    const uint4 wh = *(const uint4*)(stage + W_OFF + (uint32_t)(r0 + 8) * 128u + c);
+                    const uint32_t g4[4] = {wg.x, wg.y, wg.z, wg.w}, h4[4] = {wh.x, wh.y, wh.z, wh.w};
+#pragma unroll
+                    for (int st = 0; st < 4; ++st) {
+                        const uint32_t a0 = e4m3x2_to_bf16x2(g4[st]), a2 = e4m3x2_to_bf16x2(g4[st] >> 16);
+                        const uint32_t a1 = e4m3x2_to_bf16x2(h4[st]), a3 = e4m3x2_to_bf16x2(h4[st] >> 16);
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb) {
+                            const uint4& xv = st < 2 ? xa[nb] : xb[nb];
+                            const uint32_t b0 = (st & 1) ? xv.z : xv.x, b1 = (st & 1) ? xv.w : xv.y;
+                            mma_16816(tot[mb][nb], a0, a1, a2, a3, b0, b1);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&empty_raw[s]));
+            if (++s == RS) { s = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        float* pz = p.part + (size_t)z * p.N * p.M;
+#pragma unroll
+        for (int mb = 0; mb < 2; ++mb) {
+            const int m0 = mt * 128 + cw * 32 + mb * 16 + rho;
+            const float s0 = m0 < p.M ? (q.per_channel ? q.wscale[m0] : q.wscale[0]) : 0.f;
+            const float s1 = m0 + 8 < p.M ? (q.per_channel ? q.wscale[m0 + 8] : q.wscale[0]) : 0.f;
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                const int n0 = nb * 8 + 2 * t, n1 = n0 + 1;  // fragment columns 2t, 2t+1 are tokens 2t, 2t+1
+                if (m0 < p.M) {
+                    if (n0 < p.N) pz[(size_t)n0 * p.M + m0] = s0 * tot[mb][nb][0];
+                    if (n1 < p.N) pz[(size_t)n1 * p.M + m0] = s0 * tot[mb][nb][1];
+                }
+                if (m0 + 8 < p.M) {
+                    if (n0 < p.N) pz[(size_t)n0 * p.M + m0 + 8] = s1 * tot[mb][nb][2];
+                    if (n1 < p.N) pz[(size_t)n1 * p.M + m0 + 8] = s1 * tot[mb][nb][3];
+                }
+            }
+        }
+    }
+}
+
 // Second stage: Y[n, m] = bf16( sum_z part[z][n][m] + bias[m] + s * sum_j H[n, j] * B[j, m] ).
 __global__ void __launch_bounds__(256) fused_finalize_kernel(const float* __restrict__ part, int splits, int N, int M,
                                                              const float* __restrict__ bias,
@@ -656,7 +825,7 @@ inline size_t al256(size_t x) { return (x + 255) & ~size_t(255); }
 // X [N, K] bf16 viewed as [k-tile][token][64]: dim0 = 64 k of one tile (contiguous), dim1 = tokens
 // (stride K), dim2 = k-tiles (stride 64 elements).  A box {64, NT, KS} then lands KS k-tiles as KS
 // separate 128-byte-swizzled [NT][64] tiles.  Needs K % 64 == 0.
-CUtensorMap make_x_map3d(const void* X, int64_t N, int64_t K, int nt) {
+CUtensorMap make_x_map3d(const void* X, int64_t N, int64_t K, int nt, int ks = KS) {
     typedef CUresult (*Fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                            const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                            CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -673,7 +842,7 @@ CUtensorMap make_x_map3d(const void* X, int64_t N, int64_t K, int nt) {
     CUtensorMap m;
     cuuint64_t dims[3] = {64, (cuuint64_t)N, (cuuint64_t)(K / 64)};
     cuuint64_t strides[2] = {(cuuint64_t)K * 2, 128};
-    cuuint32_t box[3] = {64, (cuuint32_t)nt, (cuuint32_t)KS};
+    cuuint32_t box[3] = {64, (cuuint32_t)nt, (cuuint32_t)ks};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult rc = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(X), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -701,17 +870,30 @@ void launch_stream(const CUtensorMap& tmX, const FusedParams& p, int grid, cudaS
     LQ_CUDA(cudaGetLastError());
 }
 
+template <int NB>
+void launch_stream_f8(const CUtensorMap& tmX, const CUtensorMap& tmW, const StreamF8Params& q, int grid, cudaStream_t st) {
+    auto kern = stream_small_fp8_kernel<NB>;
+    LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F8_SMEM));
+    LqProf prof(LQ_K_GEMM_MAIN, st);
+    kern<<<grid, kStreamThreads, F8_SMEM, st>>>(tmX, tmW, q);
+    LQ_CUDA(cudaGetLastError());
+}
+
 }  // namespace
 
 bool lq_fused_supported(const lq_weight* w, int64_t n_tokens, int rank) {
-    return w->scheme == LQ_INT4 && n_tokens >= 1 && n_tokens <= 64 && w->K % 64 == 0 && w->M % 8 == 0 && rank <= 64;
+    if (rank > 64 || n_tokens < 1 || w->K % 64 != 0 || w->M % 8 != 0) return false;
+    if (w->scheme == LQ_INT4) return n_tokens <= 64;
+    if (w->scheme == LQ_FP8_E4M3) return n_tokens <= STREAM_NT && ((uintptr_t)w->packed & 15) == 0;
+    return false;
 }
 
 size_t lq_fused_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank) {
     size_t h = al256((size_t)n_tokens * (size_t)(rank > 0 ? rank : 1) * 4);
     size_t tok = (size_t)std::max<int64_t>(n_tokens, STREAM_NT);
-    size_t part = al256((size_t)16 * tok * (size_t)w->m_tiles * 128 * 4);
-    size_t counters = al256((size_t)w->m_tiles * 4);
+    size_t m_tiles = (size_t)((w->M + 127) / 128);
+    size_t part = al256((size_t)16 * tok * m_tiles * 128 * 4);
+    size_t counters = al256(m_tiles * 4);
     return h + part + counters + 256;
 }
 
@@ -751,7 +933,21 @@ void lq_fused_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, 
     p.X = (const __nv_bfloat16*)X;
     p.A = A;
     p.H = Hf;
-    if (stream) {  // register-dequant stream kernel, several small CTAs per SM
+    if (stream && w->scheme == LQ_FP8_E4M3) {
+        const int slots = sms * STREAM_CTAS_PER_SM - p.h_blocks;
+        p.k_tiles = (int)((K + 63) / 64);
+        p.m_tiles = (int)((M + 127) / 128);
+        p.splits = pick_splits(p.m_tiles, (p.k_tiles + 1) / 2, slots);
+        const int grid = std::min(p.m_tiles * p.splits, slots) + p.h_blocks;
+        StreamF8Params q;
+        q.base = p;
+        q.wscale = w->scales;
+        q.per_channel = w->scale_kind == LQ_SCALE_PER_CHANNEL;
+        CUtensorMap tmX = make_x_map3d(X, N, K, STREAM_NT, KS_F8);
+        CUtensorMap tmW = lq_tc_make_map_u8(w->packed, K, M, K, 128);
+        if (N <= 8) launch_stream_f8<1>(tmX, tmW, q, grid, st);
+        else launch_stream_f8<2>(tmX, tmW, q, grid, st);
+    } else if (stream) {  // register-dequant stream kernel, several small CTAs per SM
         const int slots = sms * STREAM_CTAS_PER_SM - p.h_blocks;
         p.splits = pick_splits(p.m_tiles, p.k_tiles, slots);
         const int grid = std::min(p.m_tiles * p.splits, slots) + p.h_blocks;

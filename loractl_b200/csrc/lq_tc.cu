@@ -979,6 +979,9 @@ const uint8_t* ensure_transposed(const lq_weight* w, cudaStream_t st) {
 CUtensorMap lq_tc_make_map(const void* base, int64_t inner, int64_t rows, int64_t ld, int box_rows) {
     return make_map(base, inner, rows, ld, box_rows);
 }
+CUtensorMap lq_tc_make_map_u8(const void* base, int64_t inner, int64_t rows, int64_t ld, int box_rows) {
+    return make_map(base, inner, rows, ld, box_rows, true);
+}
 int* lq_tc_status_word(int device) { return dev_ctx(device).status; }
 int lq_tc_sm_count(int device) { return dev_ctx(device).sm_count; }
 

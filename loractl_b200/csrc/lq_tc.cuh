@@ -31,6 +31,8 @@ void lq_tc_selftest_wait(int device, unsigned limit_ms, cudaStream_t st);
 // Shared with the fused small-batch kernel (lq_fused.cu).
 // 2-D bf16 tensor map over [rows, inner] (ld elements between rows), box 64 x box_rows, 128-byte swizzle.
 CUtensorMap lq_tc_make_map(const void* base, int64_t inner, int64_t rows, int64_t ld, int box_rows);
+// Same for a byte matrix: box 128 bytes x box_rows, 128-byte swizzle.
+CUtensorMap lq_tc_make_map_u8(const void* base, int64_t inner, int64_t rows, int64_t ld, int box_rows);
 int* lq_tc_status_word(int device);
 int lq_tc_sm_count(int device);
 

@@ -83,3 +83,51 @@ def test_small_batch_autograd_roundtrip():
     dx, da, db = Q.linear_bwd_raw(wq, dev(dy, torch.bfloat16), dev(x, torch.bfloat16), h, dev(a), dev(b), 1.0)
     odx, oda, odb = O.lora_linear_bwd(dy, x, dq, a, b, 1.0)
     assert reldev(host(dx), odx) <= 6e-3 and reldev(host(da), oda) <= 8e-3 and reldev(host(db), odb) <= 8e-3
+
+
+@pytest.mark.parametrize("n", [1, 8, 9, 16])
+@pytest.mark.parametrize("k,m", [(64, 128), (320, 264), (128, 136), (1024, 768)])
+@pytest.mark.parametrize("per_channel", [True, False])
+@pytest.mark.parametrize("r", [0, 16])
+def test_small_batch_forward_over_scaled_fp8_weights(n, k, m, per_channel, r):
+    """<= 16 tokens over the file's e4m3 bytes (register conversion, warp MMA): the e4m3 -> bf16
+    conversion is exact and the f32 scale multiplies the finished sums, so the only rounding against
+    the f32 oracle is the bf16 output.  Shapes cover an odd number of 64-wide k-tiles (the last
+    128-byte box is half out of range) and a ragged last row tile."""
+    from loractl_b200 import quant as Q
+
+    w = seeded((m, k), 5, 0.02)
+    x = bf16_round(seeded((n, k), 6))
+    a = seeded((k, r), 7, 1.0 / np.sqrt(k)) if r else None
+    b = seeded((r, m), 8, 0.01) if r else None
+    bias = seeded((m,), 10, 0.1)
+    wq = lb().fp8_quantize(dev(w), per_channel)
+    wq.set_bias(dev(bias))
+    dq = O.fp8_dequant(*O.fp8_quantize(w, per_channel))
+    y, h = Q.linear_fwd_raw(wq, dev(x, torch.bfloat16), dev(a) if r else None, dev(b) if r else None, 2.0)
+    lb().check_device_status()
+    oy, oh = O.lora_linear_fwd(x, dq, a, b, 2.0, bias)
+    assert y.shape == (n, m) and torch.isfinite(y).all()
+    assert reldev(host(y), oy) <= 4e-3
+    if n * m >= 1024:
+        assert O.cosine(host(y), oy) >= 0.9999
+    if r:
+        assert reldev(host(h), oh) <= 2e-5
+
+
+def test_small_batch_fp8_full_size_site_is_deterministic():
+    """BASELINE config 2's weight (12288 x 3072 e4m3, per-channel scales) at 8 and 16 tokens."""
+    from loractl_b200 import quant as Q
+
+    w = seeded((12288, 3072), 5, 0.02)
+    wq = lb().fp8_quantize(dev(w), True)
+    dq = O.fp8_dequant(*O.fp8_quantize(w, True))
+    a, b = seeded((3072, 32), 7, 1.0 / np.sqrt(3072)), seeded((32, 12288), 8, 0.01)
+    for n in (8, 16):
+        x = bf16_round(seeded((n, 3072), 6))
+        y1, _ = Q.linear_fwd_raw(wq, dev(x, torch.bfloat16), dev(a), dev(b), 1.0)
+        y2, _ = Q.linear_fwd_raw(wq, dev(x, torch.bfloat16), dev(a), dev(b), 1.0)
+        lb().check_device_status()
+        oy, _ = O.lora_linear_fwd(x, dq, a, b, 1.0)
+        assert torch.equal(y1, y2)
+        assert reldev(host(y1), oy) <= 4e-3 and O.cosine(host(y1), oy) >= 0.9999
