@@ -19,6 +19,8 @@
 // deterministic.  Scale handling: w = bf16(q * bf16(scale)); q is exact, the scale is rounded to
 // bf16 once per group (relative 2^-9), inside the bf16 path's stated tolerance.
 #include <algorithm>
+#include <cstdlib>
+#include <utility>
 
 #include <cuda_fp8.h>
 
@@ -29,6 +31,38 @@
 namespace {
 
 using namespace umma;
+
+// Programmatic dependent launch.  A site of the <= 16-token path is two short launches (weight
+// kernel, finalize) whose launch latency is comparable to their run time; both kernels therefore
+// let their successor in the stream start launching at once (`launch_dependents`) and wait for
+// their predecessor's completion and memory flush (`wait`) before touching any global memory.
+// Launched without the attribute (or after a kernel that never triggers) both are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("LQ_NO_PDL");
+        return !(e && e[0] == '1');
+    }();
+    return on;
+}
+
+// <<<grid, block, smem, st>>> with the programmatic-stream-serialization attribute.
+template <typename... KArgs, typename... Args>
+void launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    LQ_CUDA(cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...));
+}
 
 constexpr int kFusedThreads = 64 + 512;  // producer warp, MMA warp, two dequant groups of 8 warps
 constexpr int A_STAGES = 3;
@@ -421,6 +455,8 @@ stream_small_fwd_kernel(const __grid_constant__ CUtensorMap tmX, FusedParams p) 
     uint64_t* empty_raw = bars + RS;
     volatile int* abort_flag = (volatile int*)(bars + 2 * RS);
 
+    pdl_launch_dependents();
+    pdl_wait();
     if ((int)blockIdx.x < p.h_blocks) {  // uniform per CTA
         stream_h_block(p, (int)blockIdx.x, (float*)raw);
         return;
@@ -617,6 +653,8 @@ stream_small_fp8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
     uint64_t* empty_raw = bars + RS;
     volatile int* abort_flag = (volatile int*)(bars + 2 * RS);
 
+    pdl_launch_dependents();
+    pdl_wait();
     if ((int)blockIdx.x < p.h_blocks) {  // uniform per CTA
         stream_h_block(p, (int)blockIdx.x, (float*)raw);
         return;
@@ -746,6 +784,8 @@ __global__ void __launch_bounds__(256) fused_finalize_kernel(const float* __rest
                                                              const float* __restrict__ bias,
                                                              const float* __restrict__ H, const float* __restrict__ B,
                                                              int r, float s, __nv_bfloat16* __restrict__ Y) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int m = blockIdx.x * blockDim.x + threadIdx.x;
     const int n = blockIdx.y;
     if (m >= M) return;
@@ -866,7 +906,7 @@ void launch_stream(const CUtensorMap& tmX, const FusedParams& p, int grid, cudaS
     auto kern = stream_small_fwd_kernel<NB>;
     LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)STREAM_SMEM));
     LqProf prof(LQ_K_GEMM_MAIN, st);
-    kern<<<grid, kStreamThreads, STREAM_SMEM, st>>>(tmX, p);
+    launch_pdl(kern, dim3(grid), dim3(kStreamThreads), STREAM_SMEM, st, tmX, p);
     LQ_CUDA(cudaGetLastError());
 }
 
@@ -875,7 +915,7 @@ void launch_stream_f8(const CUtensorMap& tmX, const CUtensorMap& tmW, const Stre
     auto kern = stream_small_fp8_kernel<NB>;
     LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F8_SMEM));
     LqProf prof(LQ_K_GEMM_MAIN, st);
-    kern<<<grid, kStreamThreads, F8_SMEM, st>>>(tmX, tmW, q);
+    launch_pdl(kern, dim3(grid), dim3(kStreamThreads), F8_SMEM, st, tmX, tmW, q);
     LQ_CUDA(cudaGetLastError());
 }
 
@@ -965,7 +1005,11 @@ void lq_fused_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, 
     {
         LqProf prof(LQ_K_REDUCE, st);
         dim3 g((unsigned)((M + 255) / 256), (unsigned)N);
-        fused_finalize_kernel<<<g, 256, 0, st>>>(part, p.splits, (int)N, (int)M, w->bias, Hf, B, r, s, (__nv_bfloat16*)Y);
+        if (stream)
+            launch_pdl(fused_finalize_kernel, g, dim3(256), 0, st, (const float*)part, p.splits, (int)N, (int)M,
+                       (const float*)w->bias, (const float*)Hf, B, r, s, (__nv_bfloat16*)Y);
+        else
+            fused_finalize_kernel<<<g, 256, 0, st>>>(part, p.splits, (int)N, (int)M, w->bias, Hf, B, r, s, (__nv_bfloat16*)Y);
         LQ_CUDA(cudaGetLastError());
     }
 }
