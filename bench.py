@@ -38,13 +38,13 @@ WORKLOADS = {
     # name: (scheme, K = d_in, M = d_out, rank, alpha, tokens, group)
     "cfg2": ("fp8", 3072, 12288, 32, 32.0, 8192, 0),
     "cfg1": ("int4", 3072, 3072, 16, 16.0, 4096, 64),
-    # the MLP up-projection of BASELINE config 3's block, int4 block 64, rank 16, on the block's
-    # 4096 image + 512 text tokens
+    # the MLP up-projection (3072 -> 12288) of a double-stream block, int4 block 64, rank 16, on the
+    # block's 4096 image + 512 text tokens
     "cfg3up": ("int4", 3072, 12288, 16, 16.0, 4608, 64),
 }
 METRIC = "LoRA-linear fwd+bwd TFLOP/s"
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of the dominant kernel, from
-# the ncu capture summarised in profiles/umma_gemm_cfg2_step.md: forward 534.2 MB, backward
+# an ncu capture of the two frozen-GEMM launches of one step (summarised under profiles/): forward 534.2 MB, backward
 # 874.0 MB, averaged like `achieved` is over the two launches of a step.
 NCU_TRAFFIC_BYTES = {"cfg2": (534.23e6 + 873.95e6) / 2}
 
@@ -499,10 +499,10 @@ def run_ours(args):
 
 
 def run_stream(args):
-    """The packed-weight-stream regime (`--regime stream`): int4 3072 x 3072 (BASELINE config 1's
+    """The packed-weight-stream regime (`--regime stream`): int4 3072 x 3072 (the single-linear headline
     site, block 64, rank 16) forward at N in {1, 8, 16, 64} tokens.  40 distinct sites (212 MB
     of packed weights, more than the 126 MB L2; also 10 int4 and 10 scaled-fp8 12288 x 3072 sites,
-    the latter config 2's weight at 1, 8 and 16 tokens) run back to back inside one CUDA graph, so every
+    the latter the headline workload's weight at 1, 8 and 16 tokens) run back to back inside one CUDA graph, so every
     launch streams its weight from HBM and launch latency is not the thing measured.  Reports the
     algorithmic packed-stream bytes (K*M/2 + 4*K*M/64 = 5,308,416 B per site) per second, for
     the whole site (weight kernel with H = X.A folded in at N <= 16, finalize) and for the weight
@@ -524,7 +524,7 @@ def run_stream(args):
     r, s = 16, 1.0
     g = torch.Generator(device=dev).manual_seed(5)
     all_results = {}
-    # (d_out, d_in, sites): config 1's 3072 x 3072 site, and the 3072 -> 12288 MLP up-projection
+    # (d_out, d_in, sites): the cfg1 workload's 3072 x 3072 site, and the 3072 -> 12288 MLP up-projection
     # of configs 3/5 held as int4 (21.2 MB of packed weight per site)
     for m, k, sites, scheme in ((3072, 3072, 40, "int4"), (12288, 3072, 10, "int4"), (12288, 3072, 10, "fp8")):
         weights = []
@@ -593,7 +593,7 @@ def run_stream(args):
     head = all_results["3072x12288-fp8"]
     best = head["by_tokens"]["8"]
     line = {
-        "metric": "packed-weight stream GB/s (config 2 weight: scaled fp8 3072 -> 12288, forward, 8 tokens)",
+        "metric": "packed-weight stream GB/s (cfg2 weight: scaled fp8 3072 -> 12288, forward, 8 tokens)",
         "value": best["site_stream_gbs"], "unit": "GB/s", "n_gpus": 1, "steps": max(args.steps, 10), "warmup": 3,
         "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "cfg2-stream", "sites": head["sites"], "d_in": 3072, "d_out": 12288, "rank": r,
@@ -706,11 +706,12 @@ def run_load(args):
 
 
 def run_train_step(args):
-    """`--regime step`: LoRA training steps/s of a double-stream MMDiT block stack (BASELINE configs
-    3 and 5: hidden 3072, 24 heads, MLP 12288, every linear int4 block-64 + LoRA, 4096 image + 512
+    """`--regime step`: LoRA training steps/s of a double-stream MMDiT block stack (the two model
+    workloads: hidden 3072, 24 heads, MLP 12288, every linear int4 block-64 + LoRA, 4096 image + 512
     text tokens per sample, bf16 activations, block-checkpoint recompute, flow-matching MSE loss),
     data-parallel over the ranks torchrun started, LoRA gradients all-reduced in one flat bucket.
-    `--blocks` and `--batch` scale it down; the defaults are config 3 (one block, batch 1, rank 16)."""
+    `--blocks`, `--batch` and `--rank` pick the workload: the defaults are the one-block workload (batch 1,
+    rank 16); `--blocks 24 --batch 8 --rank 32` is the full stack."""
     import torch
     import torch.distributed as dist
 
@@ -795,9 +796,9 @@ def run_train_step(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--blocks", type=int, default=1, help="--regime step: blocks in the stack (config 5: 24)")
-    ap.add_argument("--batch", type=int, default=1, help="--regime step: global batch (config 5: 8)")
-    ap.add_argument("--rank", type=int, default=16, help="--regime step: LoRA rank (config 5: 32)")
+    ap.add_argument("--blocks", type=int, default=1, help="--regime step: blocks in the stack (full stack: 24)")
+    ap.add_argument("--batch", type=int, default=1, help="--regime step: global batch (full stack: 8)")
+    ap.add_argument("--rank", type=int, default=16, help="--regime step: LoRA rank (full stack: 32)")
     ap.add_argument("--regime", default="tensor", choices=["tensor", "stream", "step", "load"],
                     help="tensor: the headline fwd+bwd step; stream: packed-weight stream at <= 64 tokens; "
                          "step: LoRA training steps/s of a double-stream MMDiT block stack; "

@@ -1,4 +1,4 @@
-"""Parity at BASELINE config 2's full size: scaled-fp8 3072 -> 12288 weight with per-output-channel
+"""Parity at the headline benchmark's full size: scaled-fp8 3072 -> 12288 weight with per-output-channel
 scales, LoRA rank 32, 8192 bf16 tokens, forward and backward, through the C ABI, for both compute
 types (bf16 and native e4m3).
 

@@ -47,7 +47,7 @@ def test_fused_small_batch_forward_matches_oracle(n, k, m, block, r):
 
 
 def test_fused_full_size_site_and_determinism():
-    """BASELINE config 1's weight (3072 x 3072, int4 block 64) at 64, 16 and 1 tokens."""
+    """The single-linear benchmark's weight (3072 x 3072, int4 block 64) at 64, 16 and 1 tokens."""
     from loractl_b200 import quant as Q
 
     w = seeded((3072, 3072), 5, 0.02)
@@ -116,7 +116,7 @@ def test_small_batch_forward_over_scaled_fp8_weights(n, k, m, per_channel, r):
 
 
 def test_small_batch_fp8_full_size_site_is_deterministic():
-    """BASELINE config 2's weight (12288 x 3072 e4m3, per-channel scales) at 8 and 16 tokens."""
+    """The headline benchmark's weight (12288 x 3072 e4m3, per-channel scales) at 8 and 16 tokens."""
     from loractl_b200 import quant as Q
 
     w = seeded((12288, 3072), 5, 0.02)

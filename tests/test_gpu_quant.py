@@ -40,7 +40,7 @@ def test_codes_and_scales_bit_exact(bits, block, shape):
 
 @pytest.mark.parametrize("bits", [4, 8])
 def test_full_size_site_bit_exact(bits):
-    """BASELINE config 1's weight: 3072 x 3072, N(0, 0.02), block 64."""
+    """The single-linear benchmark's weight: 3072 x 3072, N(0, 0.02), block 64."""
     w = seeded((3072, 3072), 5, 0.02)
     wq = lb().quantize_linear_weight(dev(w), bits, 64)
     codes, scales = wq.unpack()
