@@ -780,6 +780,9 @@ stream_small_fp8_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
 }
 
 // Second stage: Y[n, m] = bf16( sum_z part[z][n][m] + bias[m] + s * sum_j H[n, j] * B[j, m] ).
+// One thread per output: at these sizes the kernel is bound by the latency of its few dependent
+// loads, so the widest possible grid wins (a variant that kept B[j, m] in registers across eight
+// tokens per thread loaded an eighth of the data and ran 1.5 to 2 times slower).
 __global__ void __launch_bounds__(256) fused_finalize_kernel(const float* __restrict__ part, int splits, int N, int M,
                                                              const float* __restrict__ bias,
                                                              const float* __restrict__ H, const float* __restrict__ B,
@@ -947,12 +950,15 @@ void lq_fused_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, 
     float* part = (float*)((char*)ws + al256((size_t)N * (size_t)(r > 0 ? r : 1) * 4));
     if (r > 0 && H_out) Hf = H_out;
     const bool stream = N <= STREAM_NT;
-    if (r > 0 && !stream) {  // H = X . A in f32: one block per token, a few MFLOP in total
-        LqProf prof(LQ_K_GEMM_DOWN, st);
+    bool forked = false;
+    if (r > 0 && !stream) {  // H = X . A in f32: one block per token, on the side stream beside the weight kernel
+        cudaStream_t hs = lq_tc_fork(w->device, st);
+        forked = true;
+        LqProf prof(LQ_K_GEMM_DOWN, hs);
         const __nv_bfloat16* Xb = (const __nv_bfloat16*)X;
-        if (r <= 16) small_h_kernel<16><<<(unsigned)N, 256, 0, st>>>(Xb, A, (int)K, r, Hf);
-        else if (r <= 32) small_h_kernel<32><<<(unsigned)N, 256, 0, st>>>(Xb, A, (int)K, r, Hf);
-        else small_h_kernel<64><<<(unsigned)N, 256, 0, st>>>(Xb, A, (int)K, r, Hf);
+        if (r <= 16) small_h_kernel<16><<<(unsigned)N, 256, 0, hs>>>(Xb, A, (int)K, r, Hf);
+        else if (r <= 32) small_h_kernel<32><<<(unsigned)N, 256, 0, hs>>>(Xb, A, (int)K, r, Hf);
+        else small_h_kernel<64><<<(unsigned)N, 256, 0, hs>>>(Xb, A, (int)K, r, Hf);
         LQ_CUDA(cudaGetLastError());
     }
     const int sms = lq_tc_sm_count(w->device);
@@ -1002,6 +1008,7 @@ void lq_fused_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, 
         if (nt == 32) launch_fused<32>(tmX, p, grid, st);
         else launch_fused<64>(tmX, p, grid, st);
     }
+    if (forked) lq_tc_join(w->device, st);
     {
         LqProf prof(LQ_K_REDUCE, st);
         dim3 g((unsigned)((M + 255) / 256), (unsigned)N);

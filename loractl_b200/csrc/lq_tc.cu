@@ -979,6 +979,16 @@ const uint8_t* ensure_transposed(const lq_weight* w, cudaStream_t st) {
 CUtensorMap lq_tc_make_map(const void* base, int64_t inner, int64_t rows, int64_t ld, int box_rows) {
     return make_map(base, inner, rows, ld, box_rows);
 }
+cudaStream_t lq_tc_fork(int device, cudaStream_t st) {
+    ForkJoin fj(dev_ctx(device), st, true);
+    fj.fork();
+    return fj.side();
+}
+void lq_tc_join(int device, cudaStream_t st) {
+    ForkJoin fj(dev_ctx(device), st, true);
+    fj.join(1);
+}
+
 CUtensorMap lq_tc_make_map_u8(const void* base, int64_t inner, int64_t rows, int64_t ld, int box_rows) {
     return make_map(base, inner, rows, ld, box_rows, true);
 }

@@ -34,6 +34,11 @@ CUtensorMap lq_tc_make_map(const void* base, int64_t inner, int64_t rows, int64_
 // Same for a byte matrix: box 128 bytes x box_rows, 128-byte swizzle.
 CUtensorMap lq_tc_make_map_u8(const void* base, int64_t inner, int64_t rows, int64_t ld, int box_rows);
 int* lq_tc_status_word(int device);
+// Event fork / join with the per-(device, caller stream) side stream: `fork` returns the stream to
+// enqueue independent work on (the caller's own stream when forking is switched off); `join` makes
+// the caller's stream wait for everything enqueued there since.
+cudaStream_t lq_tc_fork(int device, cudaStream_t st);
+void lq_tc_join(int device, cudaStream_t st);
 int lq_tc_sm_count(int device);
 
 // Fused small-batch forward (N <= 64 tokens, int4 weights): the packed weight is streamed from HBM
