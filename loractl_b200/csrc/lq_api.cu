@@ -413,7 +413,7 @@ int lq_linear_fwd(const lq_weight_t* w, const void* X, int64_t n_tokens, int dty
             return;
         }
         if (dtype == LQ_BF16 && lq_fused_supported(w, n_tokens, rank)) {
-            // packed-weight-stream regime: dequantise in shared memory, no bf16 weight in HBM
+            // packed-weight-stream regime: the weight is converted on chip, no bf16 weight in HBM
             lq_fused_fwd(w, X, n_tokens, A, B, rank, scaling, Y, H_out, workspace, workspace_bytes, st);
             return;
         }

@@ -1,23 +1,28 @@
-// Fused small-batch forward: the packed-weight-stream regime (N <= 64 tokens).
+// Small-batch forward: the packed-weight-stream regime (N <= 64 tokens).
 //
 // At N <= 64 the frozen GEMM is bound by the HBM stream of the packed weight (int4: half a byte
-// per element), so the weight is read from HBM exactly once, as packed tiles, and dequantised in
-// shared memory on its way into tcgen05.mma — no bf16 copy of the weight ever exists in HBM.
+// per element; scaled fp8: one), so the weight is read from HBM exactly once, as stored, and
+// converted on chip — no bf16 copy of the weight ever exists in HBM.  Three kernels share the work
+// decomposition (128-row weight tile x k-split -> f32 partial tile; `fused_finalize_kernel` sums the
+// splits in a fixed order and adds bias and s * (X.A) . B, so results are deterministic):
 //
-//   roles swapped w.r.t. the large-N kernel: the weight tile is the 128-row MMA operand,
-//   the token tile is the narrow one:   D[128 features, NT tokens] += Wt[128, 64] . Xt[NT, 64]^T
+//   stream_small_fwd_kernel   int4, N <= 16: packed words -> registers -> mma.sync (see its header)
+//   stream_small_fp8_kernel   scaled fp8, N <= 16: e4m3 bytes -> registers -> mma.sync
+//   fused_small_fwd_kernel    int4, 17 <= N <= 64: dequantise into a shared-memory operand tile,
+//                             tcgen05.mma with the weight tile as the 128-row operand (below)
 //
-//   warp 0      producer: cp.async.bulk of one packed tile (4 KB) + its scales, TMA tile of X
+// fused_small_fwd_kernel:  D[128 features, NT tokens] += Wt[128, 64] . Xt[NT, 64]^T
+//
+//   warp 0      producer: cp.async.bulk of KS packed tiles (16 KB) + their scales, one 3-D TMA box of X
 //   warp 1      MMA issuer (tcgen05.mma 128 x NT x 16, f32 accumulator in TMEM)
-//   warps 2-9   dequant: nibbles -> exact bf16 integers (0x4300 | u is 128 + u; minus 136) times
-//               the group scale, written straight into the 128-byte-swizzled K-major operand
-//               layout (generic-proxy stores + fence.proxy.async); afterwards the same warps
-//               drain TMEM and store the item's partial tile
+//   warps 2-17  dequant, two groups of 8 warps on alternate k-tiles: nibbles -> exact bf16 integers
+//               (0x4300 | u is 128 + u; minus 136) times the group scale, written straight into the
+//               128-byte-swizzled K-major operand layout (generic-proxy stores + fence.proxy.async);
+//               group 0 afterwards drains TMEM and stores the item's partial tile
 //
-// Work items are (128-row weight tile, k-split); partial tiles are f32 and a second kernel sums
-// the splits in a fixed order and adds bias and the LoRA term s * (X.A) . B, so results are
-// deterministic.  Scale handling: w = bf16(q * bf16(scale)); q is exact, the scale is rounded to
-// bf16 once per group (relative 2^-9), inside the bf16 path's stated tolerance.
+// Scale handling there: w = bf16(q * bf16(scale)); q is exact, the scale is rounded to bf16 once per
+// group (relative 2^-9), inside the bf16 path's stated tolerance.  The two register kernels apply
+// the f32 scale to f32 sums instead and round no weight at all.
 #include <algorithm>
 #include <cstdlib>
 #include <utility>

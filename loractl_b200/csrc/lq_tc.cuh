@@ -41,8 +41,9 @@ cudaStream_t lq_tc_fork(int device, cudaStream_t st);
 void lq_tc_join(int device, cudaStream_t st);
 int lq_tc_sm_count(int device);
 
-// Fused small-batch forward (N <= 64 tokens, int4 weights): the packed weight is streamed from HBM
-// exactly once and dequantised in shared memory on its way into tcgen05.mma.
+// Small-batch forward (int4 weights at N <= 64 tokens, scaled-fp8 weights at N <= 16): the packed
+// weight is streamed from HBM exactly once and converted on chip (registers + mma.sync at N <= 16,
+// shared memory + tcgen05.mma above).
 bool lq_fused_supported(const lq_weight* w, int64_t n_tokens, int rank);
 size_t lq_fused_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank);
 void lq_fused_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, const float* B, int r, float s,
