@@ -360,6 +360,236 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
     }
 }
 
+// ---- CTA-pair variant of the frozen GEMM -------------------------------------------------
+//
+// Two CTAs of a cluster (an SM pair) share one 256 x BLOCK_N output tile: each CTA loads its own
+// 128 rows of A and HALF of the B tile (BLOCK_N / 2 rows), one thread of the even CTA issues
+// tcgen05.mma.cta_group::2 with M = 256, and each CTA's TMEM receives the 128 accumulator rows of
+// its own A half.  Per FLOP every SM therefore stages and reads half of the B operand it does in
+// the single-CTA kernel (64 B instead of 96 B of shared memory per clock at 256 columns), which is
+// what the tensor pipe waits on and what the power budget goes into.
+//
+// Barrier protocol (every CTA holds the same barrier objects at the same offsets):
+//   full[s]    used in the leader only: the leader's producer arms it with the bytes of BOTH CTAs'
+//              copies; each CTA's copies signal it (the peer's through the pair-relative address)
+//   empty[s]   one arrival per use in BOTH CTAs, from the leader's multicast tcgen05.commit
+//   tfull[a]   same, accumulator complete
+//   tempty[a]  used in the leader only: 512 arrivals, the epilogue threads of both CTAs
+// K-major bf16 (or e4m3) operands, bf16 output through TMA stores, no split: the two frozen GEMMs.
+template <int BLOCK_N>
+struct Cfg2 {
+    static constexpr uint32_t A_BYTES = BM * BK * 2;
+    static constexpr uint32_t B_BYTES = (BLOCK_N / 2) * BK * 2;  // this CTA's half of the B tile
+    static constexpr int STAGES = (208 * 1024 - 16 * 1024) / (A_BYTES + B_BYTES);
+    static constexpr uint32_t TMEM_COLS = BLOCK_N * 2 <= 256 ? 256 : 512;
+    static constexpr uint32_t STAGE_OUT = 8 * 2048;
+    static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + STAGE_OUT + 1024 + 256;
+};
+
+template <int BLOCK_N, bool F8>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
+                  const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
+                  const __grid_constant__ CUtensorMap tmC, GemmParams p) {
+    using C = Cfg2<BLOCK_N>;
+    constexpr int STAGES = C::STAGES;
+    constexpr int BK0 = F8 ? 128 : BK;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + (size_t)STAGES * C::A_BYTES;
+    uint8_t* stage_out = smem + (size_t)STAGES * (C::A_BYTES + C::B_BYTES);
+    uint64_t* bars = (uint64_t*)(stage_out + C::STAGE_OUT);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + STAGES;
+    uint64_t* tfull = bars + 2 * STAGES;
+    uint64_t* tempty = bars + 2 * STAGES + 2;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();  // 0: leader (issues the MMAs), 1: peer
+    const bool leader = rank == 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full[s]), 1);
+            mbar_init(smem_u32(&empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&tfull[a]), 1);
+            mbar_init(smem_u32(&tempty[a]), 512);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tmA0);
+        prefetch_tmap(&tmB0);
+        prefetch_tmap(&tmA1);
+        prefetch_tmap(&tmB1);
+    }
+    if (warp == 1) {  // the same warp of both CTAs, the same slot offset
+        tmem_alloc2(smem_u32(tmem_slot), C::TMEM_COLS);
+        tmem_relinquish2();
+    }
+    tc_fence_before();
+    cluster_sync_all();  // barriers of both CTAs are initialised before either signals the other's
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int kb_total = p.kb0 + p.kb1;
+    const int num_items = p.m_tiles * p.n_tiles;  // m_tiles counts 256-row pair tiles here
+    const int cid = (int)(blockIdx.x >> 1), ncl = (int)(gridDim.x >> 1);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- TMA producer (both CTAs) ----------------
+            int s = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int item = cid; ok && item < num_items; item += ncl) {
+                int m_tile, n_tile, z;
+                item_coords(p, item, m_tile, n_tile, z);
+                for (int kb = 0; kb < kb_total; ++kb) {
+                    if (!mbar_wait(smem_u32(&empty[s]), phase ^ 1u, abort_flag, p.status, 51)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(&full[s]);
+                    if (leader) mbar_expect_tx(bar, 2 * (C::A_BYTES + C::B_BYTES));
+                    const bool ext = kb >= p.kb0;
+                    const CUtensorMap* ma = ext ? &tmA1 : &tmA0;
+                    const CUtensorMap* mb = ext ? &tmB1 : &tmB0;
+                    const int kc = ext ? (kb - p.kb0) * BK : kb * BK0;
+                    tma_load_2d_pair(smem_u32(smem_a + (size_t)s * C::A_BYTES), ma, bar, kc, m_tile * 256 + (int)rank * BM);
+                    tma_load_2d_pair(smem_u32(smem_b + (size_t)s * C::B_BYTES), mb, bar, kc,
+                                     n_tile * BLOCK_N + (int)rank * (BLOCK_N / 2));
+                    if (++s == STAGES) { s = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok)
+                for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            // ---------------- MMA issuer (leader CTA only) ----------------
+            constexpr uint32_t idesc = make_idesc(1, 1, false, false, 256, BLOCK_N);
+            constexpr uint32_t idesc8 = make_idesc(0, 0, false, false, 256, BLOCK_N);
+            const uint32_t d_hi = desc_hi(1024);
+            const uint32_t a_lo0 = desc_lo(smem_u32(smem_a), 16);
+            const uint32_t b_lo0 = desc_lo(smem_u32(smem_b), 16);
+            int s = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int item = cid; ok && item < num_items; item += ncl) {
+                if (!mbar_wait(smem_u32(&tempty[acc]), acc_phase ^ 1u, abort_flag, p.status, 52)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BLOCK_N);
+                for (int kb = 0; kb < kb_total; ++kb) {
+                    if (!mbar_wait(smem_u32(&full[s]), phase, abort_flag, p.status, 53)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_lo = a_lo0 + (uint32_t)s * (C::A_BYTES >> 4);
+                    const uint32_t b_lo = b_lo0 + (uint32_t)s * (C::B_BYTES >> 4);
+                    if (F8 && kb < p.kb0) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            mma2_f8(tmem_d, desc_join(a_lo + k * 2u, d_hi), desc_join(b_lo + k * 2u, d_hi), idesc8,
+                                    (kb > 0 || k > 0) ? 1u : 0u);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < BK / 16; ++k)
+                            mma2_f16(tmem_d, desc_join(a_lo + k * 2u, d_hi), desc_join(b_lo + k * 2u, d_hi), idesc,
+                                     (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    mma2_commit_mc(smem_u32(&empty[s]), 3);  // frees the stage in both CTAs
+                    if (++s == STAGES) { s = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                mma2_commit_mc(smem_u32(&tfull[acc]), 3);  // accumulator complete -> both epilogues
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..9 of both CTAs, each its own 128 rows) ----------------
+        const int quarter = warp & 3;
+        const int chalf = (warp - 2) >> 2;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int item = cid; ok && item < num_items; item += ncl) {
+            int m_tile, n_tile, z;
+            item_coords(p, item, m_tile, n_tile, z);
+            if (!mbar_wait(smem_u32(&tfull[acc]), acc_phase, abort_flag, p.status, 54)) { ok = false; break; }
+            tc_fence_after();
+            const int row0 = m_tile * 256 + (int)rank * BM + quarter * 32;
+            const int row = row0 + lane;
+            const float rs = (p.row_scale && row < p.Mg) ? p.row_scale[row] : 1.f;
+#pragma unroll 1
+            for (int c = 0; c < BLOCK_N / 64; ++c) {
+                uint32_t r[32];
+                const int cc = chalf * (BLOCK_N / 2) + c * 32;
+                tmem_ld_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N + cc), r);
+                tmem_ld_wait();
+                const int col0 = n_tile * BLOCK_N + cc;
+                uint32_t wds[16];
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    const int col = col0 + j;
+                    float v[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+                    if (col < p.Ng) {
+                        if (p.col_scale && !p.col_scale_bcast) {
+                            const float4 c0 = *(const float4*)(p.col_scale + col);
+                            const float4 c1 = *(const float4*)(p.col_scale + col + 4);
+                            const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[e] *= rs * cs[e];
+                        } else if (p.row_scale || p.col_scale) {
+                            const float sc = p.col_scale ? rs * p.col_scale[0] : rs;
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[e] *= sc;
+                        }
+                        if (p.bias) {
+                            const float4 b0 = *(const float4*)(p.bias + col);
+                            const float4 b1 = *(const float4*)(p.bias + col + 4);
+                            const float bs[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[e] += bs[e];
+                        }
+                    }
+#pragma unroll
+                    for (int e = 0; e < 8; e += 2) {
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[e], v[e + 1]);
+                        wds[(j + e) >> 1] = *(uint32_t*)&h2;
+                    }
+                }
+                uint8_t* my_stage = stage_out + (warp - 2) * 2048;
+                if (lane == 0) bulk_wait_read0();
+                __syncwarp();
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    *(uint4*)(my_stage + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) =
+                        make_uint4(wds[4 * q], wds[4 * q + 1], wds[4 * q + 2], wds[4 * q + 3]);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(&tmC, smem_u32(my_stage), col0, row0);
+                    bulk_commit();
+                }
+            }
+            tc_fence_before();
+            if (leader) mbar_arrive(smem_u32(&tempty[acc]));
+            else mbar_arrive_leader(smem_u32(&tempty[acc]));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+        if (lane == 0) bulk_wait0();
+    }
+
+    tc_fence_before();
+    cluster_sync_all();  // neither CTA leaves (and frees shared memory / TMEM) while the other may still signal it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc2(tmem_base, C::TMEM_COLS);
+    }
+}
+
 // ---- small elementwise helpers ----------------------------------------------------------
 
 // out[i * ldo + j] = bf16(alpha * in[i * si + j * sj] / div_i) for j < J, 0 for J <= j < Jpad, where
@@ -614,6 +844,81 @@ void launch_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand
     LQ_CUDA(cudaGetLastError());
 }
 
+bool pair_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("LQ_GEMM_1CTA");
+        return !(e && e[0] == '1');
+    }();
+    return on;
+}
+
+// The frozen GEMM on CTA pairs: 256 x BLOCK_N tiles, K-major operands, bf16 output through TMA stores.
+template <int BLOCK_N, bool F8>
+void launch_gemm_pair(const Operand& a0, const Operand& b0, int64_t K0, const Operand* a1, const Operand* b1, int64_t K1,
+                      __nv_bfloat16* Cout, int64_t ldc, int64_t Mg, int64_t Ng, const float* bias, cudaStream_t st,
+                      EpiScales sc = EpiScales()) {
+    using C = Cfg2<BLOCK_N>;
+    int dev;
+    LQ_CUDA(cudaGetDevice(&dev));
+    DevCtx& ctx = dev_ctx(dev);
+    CUtensorMap tA0 = make_map(a0.ptr, K0, Mg, a0.ld, BM, F8);
+    CUtensorMap tB0 = make_map(b0.ptr, K0, Ng, b0.ld, BLOCK_N / 2, F8);
+    CUtensorMap tA1 = a1 ? make_map(a1->ptr, K1, Mg, a1->ld, BM) : tA0;
+    CUtensorMap tB1 = b1 ? make_map(b1->ptr, K1, Ng, b1->ld, BLOCK_N / 2) : tB0;
+    constexpr int BK0 = F8 ? 128 : BK;
+    GemmParams p;
+    p.Mg = (int)Mg;
+    p.Ng = (int)Ng;
+    p.kb0 = (int)((K0 + BK0 - 1) / BK0);
+    p.kb1 = a1 ? (int)((K1 + BK - 1) / BK) : 0;
+    p.m_tiles = (int)((Mg + 255) / 256);  // pair tiles
+    p.n_tiles = (int)((Ng + BLOCK_N - 1) / BLOCK_N);
+    p.splits = 1;
+    p.C = Cout;
+    p.ldc = ldc;
+    p.split_stride = 0;
+    p.bias = bias;
+    p.status = ctx.status;
+    p.row_scale = sc.row;
+    p.col_scale = sc.col;
+    p.col_scale_bcast = sc.col_bcast;
+    p.tma_store = 1;
+    CUtensorMap tC = make_store_map(Cout, Ng, Mg, ldc);
+    const long long items = (long long)p.m_tiles * p.n_tiles;
+    auto kern = umma_gemm2_kernel<BLOCK_N, F8>;
+    LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+    // persistent grid = the number of CTA pairs that can be resident at once (asked once per device)
+    static std::mutex mu;
+    static int pairs_by_dev[kMaxDevices] = {};
+    int pairs;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (pairs_by_dev[dev] == 0) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(ctx.sm_count & ~1);
+            cfg.blockDim = dim3(kThreads);
+            cfg.dynamicSmemBytes = C::SMEM;
+            int n = 0;
+            LQ_CUDA(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+            pairs_by_dev[dev] = std::max(1, std::min(n, ctx.sm_count / 2));
+        }
+        pairs = pairs_by_dev[dev];
+    }
+    const int grid = 2 * (int)std::min<long long>(items, pairs);
+    LqProf prof(LQ_K_GEMM_MAIN, st);
+    kern<<<grid, kThreads, C::SMEM, st>>>(tA0, tB0, tA1, tB1, tC, p);
+    LQ_CUDA(cudaGetLastError());
+}
+
+// Tile width for the pair kernel: how well 256 x bn tiles fill the waves of sm_count / 2 pairs.
+inline double pair_waves_eff(int64_t Mg, int64_t Ng, int bn, int sm_count) {
+    const int64_t pairs = sm_count / 2;
+    const int64_t tiles = ((Mg + 255) / 256) * ((Ng + bn - 1) / bn);
+    const int64_t rounds = (tiles + pairs - 1) / pairs;
+    const double pad = (double)Ng / (double)(((Ng + bn - 1) / bn) * bn);
+    return pad * (double)tiles / (double)(rounds * pairs);
+}
+
 int choose_splits(int64_t out_tiles, int64_t k_blocks, int sm_count) {
     int64_t s = (2 * (int64_t)sm_count + out_tiles - 1) / out_tiles;
     if (s > k_blocks) s = k_blocks;
@@ -721,6 +1026,15 @@ void main_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand* 
     // Tile width: 128 x 256 is the efficient shape (96 B/clk of operand traffic per SM); 128 x 128
     // needs 128 B/clk and measured 1.5x slower per FLOP.  128 x 192 sits close to 256 and is taken
     // when it fills the last wave of the persistent grid markedly better.
+    if constexpr (sizeof(OutT) == 2) {
+        if (pair_enabled() && Mg >= 256 && Ng > 192 && sm_count >= 2) {  // the frozen GEMMs proper: CTA pairs
+            if (pair_waves_eff(Mg, Ng, 256, sm_count) >= 0.95 * pair_waves_eff(Mg, Ng, 192, sm_count))
+                launch_gemm_pair<256, false>(a0, b0, K0, a1, b1, K1, (__nv_bfloat16*)Cout, ldc, Mg, Ng, bias, st);
+            else
+                launch_gemm_pair<192, false>(a0, b0, K0, a1, b1, K1, (__nv_bfloat16*)Cout, ldc, Mg, Ng, bias, st);
+            return;
+        }
+    }
     const int64_t m_tiles = (Mg + BM - 1) / BM;
     auto waves_eff = [&](int bn) {
         const int64_t tiles = m_tiles * ((Ng + bn - 1) / bn);
@@ -943,6 +1257,13 @@ void main_gemm_f8(const Operand& a0, const Operand& b0, int64_t K0, const Operan
         return pad * (double)tiles / (double)(rounds * sm_count);
     };
     using T = __nv_bfloat16;
+    if (pair_enabled() && Mg >= 256 && Ng > 192 && sm_count >= 2) {
+        if (pair_waves_eff(Mg, Ng, 256, sm_count) >= 0.95 * pair_waves_eff(Mg, Ng, 192, sm_count))
+            launch_gemm_pair<256, true>(a0, b0, K0, a1, b1, K1, Cout, ldc, Mg, Ng, bias, st, sc);
+        else
+            launch_gemm_pair<192, true>(a0, b0, K0, a1, b1, K1, Cout, ldc, Mg, Ng, bias, st, sc);
+        return;
+    }
     if (Ng <= 128)
         launch_gemm<128, false, false, T, true>(a0, b0, K0, a1, b1, K1, Cout, ldc, 0, Mg, Ng, 1, bias, st, -1, LQ_K_GEMM_MAIN, sc);
     else if (Ng > 192 && waves_eff(256) >= 0.95 * waves_eff(192))
