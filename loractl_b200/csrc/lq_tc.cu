@@ -52,6 +52,7 @@ struct GemmParams {
     const float* col_scale;
     int col_scale_bcast;
     int tma_store;  // bf16 output leaves through shared memory and TMA tensor stores (full 64-byte row pieces)
+    int group_m;       // m-tiles per raster group (0 = 16)
 };
 
 template <int BLOCK_N>
@@ -69,7 +70,7 @@ __device__ __forceinline__ void item_coords(const GemmParams& p, int item, int& 
     const int tiles = p.m_tiles * p.n_tiles;
     z = item / tiles;
     int t = item - z * tiles;
-    constexpr int GROUP = 16;  // m-tiles per raster group: keeps a 16-tile band of A hot in L2
+    const int GROUP = p.group_m > 0 ? p.group_m : 16;  // m-tiles per raster group: a band of A kept hot in L2
     int per_group = GROUP * p.n_tiles;
     int g = t / per_group;
     int first_m = g * GROUP;
@@ -833,6 +834,7 @@ void launch_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand
     p.col_scale_bcast = sc.col_bcast;
     // bf16 output (never split): 32 x 32 boxes, 64-byte swizzle, stored by TMA
     p.tma_store = (sizeof(OutT) == 2 && splits == 1) ? 1 : 0;
+    p.group_m = 0;
     CUtensorMap tC = tA0;
     if (p.tma_store) tC = make_store_map(Cout, Ng, Mg, ldc);
     long long items = (long long)p.m_tiles * p.n_tiles * splits;
@@ -885,6 +887,21 @@ void launch_gemm_pair(const Operand& a0, const Operand& b0, int64_t K0, const Op
     p.tma_store = 1;
     CUtensorMap tC = make_store_map(Cout, Ng, Mg, ldc);
     const long long items = (long long)p.m_tiles * p.n_tiles;
+    {
+        // Raster: the CTAs of a wave run through K in step, so a wave reads each of its distinct A and
+        // B row bands from DRAM once.  With 16-pair-tile groups a wave is 16 bands of A and ncl/16 of B;
+        // when that exceeds what L2 keeps comfortably (long K) and the whole B operand is small enough
+        // to stay resident, waves instead span ALL column tiles of a few A bands: B is then read from
+        // DRAM once for the whole launch and A streams through.
+        const int ncl_est = std::max(1, ctx.sm_count / 2);
+        const double esz = F8 ? 1.0 : 2.0;
+        const double wave16 = (16.0 * 256 + (double)ncl_est / 16 * BLOCK_N) * (double)K0 * esz;
+        const double whole_b = (double)Ng * (double)K0 * esz;
+        p.group_m = 16;
+        if (wave16 > 48e6 && whole_b <= 90e6) p.group_m = std::max(1, (ncl_est + p.n_tiles - 1) / p.n_tiles);
+        static const int forced = [] { const char* e = getenv("LQ_GROUP_M"); return e ? atoi(e) : 0; }();
+        if (forced > 0) p.group_m = forced;
+    }
     auto kern = umma_gemm2_kernel<BLOCK_N, F8>;
     LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
     // persistent grid = the number of CTA pairs that can be resident at once (asked once per device)
@@ -911,7 +928,12 @@ void launch_gemm_pair(const Operand& a0, const Operand& b0, int64_t K0, const Op
 }
 
 // Tile width for the pair kernel: how well 256 x bn tiles fill the waves of sm_count / 2 pairs.
+inline int forced_pair_bn() {
+    static const int v = [] { const char* e = getenv("LQ_PAIR_BN"); return e ? atoi(e) : 0; }();
+    return v;
+}
 inline double pair_waves_eff(int64_t Mg, int64_t Ng, int bn, int sm_count) {
+    if (forced_pair_bn() == bn) return 2.0;
     const int64_t pairs = sm_count / 2;
     const int64_t tiles = ((Mg + 255) / 256) * ((Ng + bn - 1) / bn);
     const int64_t rounds = (tiles + pairs - 1) / pairs;

@@ -199,12 +199,13 @@ __device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t cols) {
 // 2-D tiled load issued by either CTA of a pair into its OWN shared memory; the bytes are counted on
 // the leader CTA's barrier (`bar` is this CTA's address of the barrier object; the peer bit is cleared
 // here).  No multicast.
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1) {
-    const uint64_t evict_normal = 0x1000000000000000ull;
+constexpr uint64_t kEvictNormal = 0x1000000000000000ull;  // L2 cache-hint operand: normal eviction priority
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1,
+                                                 uint64_t hint = kEvictNormal) {
     asm volatile(
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
         " [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(dst),
-        "l"((uint64_t)m), "r"(bar & kPeerBitMask), "r"(c0), "r"(c1), "l"(evict_normal)
+        "l"((uint64_t)m), "r"(bar & kPeerBitMask), "r"(c0), "r"(c1), "l"(hint)
         : "memory");
 }
 // D[tmem of both CTAs] (+)= A . B over the pair: M = 256 (128 rows from each CTA's A tile), each CTA's
