@@ -927,18 +927,23 @@ void launch_gemm_pair(const Operand& a0, const Operand& b0, int64_t K0, const Op
     LQ_CUDA(cudaGetLastError());
 }
 
-// Tile width for the pair kernel: how well 256 x bn tiles fill the waves of sm_count / 2 pairs.
+// Tile width for the pair kernel.  Measured on config 2's backward (512 tiles of 192 columns in 7
+// rounds of 74 pairs against 384 tiles of 256 columns in 6): a 192-column tile takes about as long
+// as a 256-column one (the MMA does not get cheaper in proportion), so what counts is the number of
+// rounds; 192 is taken only when it saves rounds or padding columns outright.
 inline int forced_pair_bn() {
     static const int v = [] { const char* e = getenv("LQ_PAIR_BN"); return e ? atoi(e) : 0; }();
     return v;
 }
-inline double pair_waves_eff(int64_t Mg, int64_t Ng, int bn, int sm_count) {
-    if (forced_pair_bn() == bn) return 2.0;
-    const int64_t pairs = sm_count / 2;
-    const int64_t tiles = ((Mg + 255) / 256) * ((Ng + bn - 1) / bn);
-    const int64_t rounds = (tiles + pairs - 1) / pairs;
-    const double pad = (double)Ng / (double)(((Ng + bn - 1) / bn) * bn);
-    return pad * (double)tiles / (double)(rounds * pairs);
+inline int pair_block_n(int64_t Mg, int64_t Ng, int sm_count) {
+    if (forced_pair_bn() == 192 || forced_pair_bn() == 256) return forced_pair_bn();
+    const int64_t pairs = std::max(1, sm_count / 2);
+    auto cost = [&](int bn) {
+        const int64_t tiles = ((Mg + 255) / 256) * ((Ng + bn - 1) / bn);
+        const int64_t rounds = (tiles + pairs - 1) / pairs;
+        return (double)rounds * (bn == 256 ? 1.0 : 0.95);
+    };
+    return cost(192) < cost(256) ? 192 : 256;
 }
 
 int choose_splits(int64_t out_tiles, int64_t k_blocks, int sm_count) {
@@ -1050,7 +1055,7 @@ void main_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand* 
     // when it fills the last wave of the persistent grid markedly better.
     if constexpr (sizeof(OutT) == 2) {
         if (pair_enabled() && Mg >= 256 && Ng > 192 && sm_count >= 2) {  // the frozen GEMMs proper: CTA pairs
-            if (pair_waves_eff(Mg, Ng, 256, sm_count) >= 0.95 * pair_waves_eff(Mg, Ng, 192, sm_count))
+            if (pair_block_n(Mg, Ng, sm_count) == 256)
                 launch_gemm_pair<256, false>(a0, b0, K0, a1, b1, K1, (__nv_bfloat16*)Cout, ldc, Mg, Ng, bias, st);
             else
                 launch_gemm_pair<192, false>(a0, b0, K0, a1, b1, K1, (__nv_bfloat16*)Cout, ldc, Mg, Ng, bias, st);
@@ -1280,7 +1285,7 @@ void main_gemm_f8(const Operand& a0, const Operand& b0, int64_t K0, const Operan
     };
     using T = __nv_bfloat16;
     if (pair_enabled() && Mg >= 256 && Ng > 192 && sm_count >= 2) {
-        if (pair_waves_eff(Mg, Ng, 256, sm_count) >= 0.95 * pair_waves_eff(Mg, Ng, 192, sm_count))
+        if (pair_block_n(Mg, Ng, sm_count) == 256)
             launch_gemm_pair<256, true>(a0, b0, K0, a1, b1, K1, Cout, ldc, Mg, Ng, bias, st, sc);
         else
             launch_gemm_pair<192, true>(a0, b0, K0, a1, b1, K1, Cout, ldc, Mg, Ng, bias, st, sc);
