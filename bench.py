@@ -44,9 +44,9 @@ WORKLOADS = {
 }
 METRIC = "LoRA-linear fwd+bwd TFLOP/s"
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of the dominant kernel, from
-# an ncu capture of the two frozen-GEMM launches of one step (summarised under profiles/): forward 534.2 MB, backward
-# 874.0 MB, averaged like `achieved` is over the two launches of a step.
-NCU_TRAFFIC_BYTES = {"cfg2": (534.23e6 + 873.95e6) / 2}
+# an ncu capture of the two frozen-GEMM launches of one step (summarised under profiles/): forward 395.1 MB, backward
+# 833.0 MB, averaged like `achieved` is over the two launches of a step.
+NCU_TRAFFIC_BYTES = {"cfg2": (395.07e6 + 832.96e6) / 2}
 
 
 def step_flops(n, k, m, r):
@@ -461,7 +461,7 @@ def run_ours(args):
         gm_ms, gm_n = kinds.get("gemm_main", (0.0, 0))
         achieved = (main_gemm_flops(n, k, m, r) / 2) / (gm_ms / max(gm_n, 1) * 1e-3) / 1e12 if gm_n else None
         roofline = {
-            "bound": "tensor", "kernel": "umma_gemm_kernel (frozen GEMM + fused LoRA K extension)",
+            "bound": "tensor", "kernel": "umma_gemm2_kernel (frozen GEMM on CTA pairs + fused LoRA K extension)",
             "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": (achieved / peak) if achieved else None,
             "peak_source": peak_src, "traffic": None if fp8c else NCU_TRAFFIC_BYTES.get(wl),
             "traffic_unit": "bytes per launch (ncu, full-size launch)",
