@@ -28,6 +28,11 @@
 extern "C" {
 #endif
 
+/* The library is built with hidden default visibility; only what this header declares is exported. */
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
 #define LQ_ABI_VERSION 1
 
 typedef enum lq_status {
@@ -269,7 +274,7 @@ int lq_profile_collect(double* ms_by_kind, uint64_t* launches_by_kind, int n_kin
  * roofline probes: C[Mg, Ng] = A . B^T + bias with bf16 operands and f32 accumulation.
  * An operand is K-major ([rows, Kg], Kg contiguous; *_mn = 0) or MN-major ([Kg, rows], rows
  * contiguous; *_mn = 1); ld* are row strides in elements.  block_n is 64, 128 or 256;
- * splits > 1 needs c_dtype LQ_F32, block_n 64 and `partial_ws` of
+ * splits > 1 needs c_dtype LQ_F32, block_n 64, splits <= ceil(Kg / 64) and `partial_ws` of
  * splits * Mg * roundup(Ng, 64) floats.  The reference has no counterpart: burn's
  * `float_matmul` (crates/loractl-core/src/quant.rs:233,251) is the nearest equivalent. */
 int lq_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, int64_t ldb,
@@ -294,10 +299,15 @@ int lq_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, 
  * the SM count; make that first call before any stream capture begins.
  * Every call on a GPU shares the one array and it keeps the previous call's contents: calls that
  * may overlap on the GPU (different streams without ordering) race and must be serialised by the
- * caller.  If a bounded device-side wait gives up, every element of C is NaN. */
+ * caller.  If a bounded device-side wait gives up, every element of C is NaN and the next
+ * lq_check_device_status() on that device returns LQ_ERR_TIMEOUT. */
 int lq_gemm_bf16_splitk_static(const void* A, const void* B, int operands_mn, int64_t lda, int64_t ldb,
                                float* C, int64_t ldc, int64_t Mg, int64_t Ng, int64_t Kg, int splits,
                                void* stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
 
 #ifdef __cplusplus
 }

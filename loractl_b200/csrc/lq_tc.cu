@@ -39,20 +39,20 @@ constexpr int BK = 64;
 constexpr int kThreads = 320;  // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quarter)
 
 struct GemmParams {
-    int Mg, Ng;
-    int kb0, kb1;
-    int m_tiles, n_tiles, splits;
-    void* C;
-    long long ldc, split_stride;
-    const float* bias;
-    int* status;
+    int Mg = 0, Ng = 0;
+    int kb0 = 0, kb1 = 0;
+    int m_tiles = 0, n_tiles = 0, splits = 1;
+    void* C = nullptr;
+    long long ldc = 0, split_stride = 0;
+    const float* bias = nullptr;
+    int* status = nullptr;
     // optional epilogue scales: v = acc * row_scale[row] * col_scale[col] (NULL = 1); with
     // col_scale_bcast the single value col_scale[0] applies to every column
-    const float* row_scale;
-    const float* col_scale;
-    int col_scale_bcast;
-    int tma_store;  // bf16 output leaves through shared memory and TMA tensor stores (full 64-byte row pieces)
-    int group_m;       // m-tiles per raster group (0 = 16)
+    const float* row_scale = nullptr;
+    const float* col_scale = nullptr;
+    int col_scale_bcast = 0;
+    int tma_store = 0;  // bf16 output leaves through shared memory and TMA tensor stores (full 64-byte row pieces)
+    int group_m = 0;    // m-tiles per raster group (0 = 16)
 };
 
 template <int BLOCK_N>
@@ -1353,13 +1353,16 @@ size_t lq_tc_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank) {
     return carve_tc(w, n_tokens, rank, nullptr, 148).bytes;
 }
 
+int lq_static_read_sticky(int device);  // the allocation-free split contraction's own error word (below)
+
 int lq_tc_read_status(int device, cudaStream_t st) {
     DevCtx& c = dev_ctx(device);
     int v = 0;
     LQ_CUDA(cudaStreamSynchronize(st));
     LQ_CUDA(cudaMemcpy(&v, c.status, sizeof(int), cudaMemcpyDeviceToHost));
     if (v != 0) LQ_CUDA(cudaMemset(c.status, 0, sizeof(int)));
-    return v;
+    const int v2 = lq_static_read_sticky(device);
+    return v != 0 ? v : v2;
 }
 
 void lq_tc_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, const float* B, int r, float s, void* Y,
@@ -1598,6 +1601,8 @@ void lq_tc_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B, int b_
     LQ_CHECK_ARG(((uintptr_t)bias & 15) == 0, "gemm: bias must be 16-byte aligned");
     if (splits > 1) {
         LQ_CHECK_ARG(c_dtype == LQ_F32 && partial_ws != nullptr && block_n == 64, "split gemm: f32 out, block_n 64");
+        // an empty k-range would publish an accumulator no MMA ever wrote
+        LQ_CHECK_ARG(splits <= (Kg + BK - 1) / BK, "split gemm: splits must not exceed ceil(Kg / 64)");
         int64_t ldp = ((Ng + 63) / 64) * 64;
         if (a_mn && b_mn)
             launch_gemm<64, true, true, float>(a, b, Kg, nullptr, nullptr, 0, partial_ws, ldp, Mg * ldp, Mg, Ng, splits, nullptr, st);
@@ -1647,6 +1652,7 @@ namespace {
 constexpr size_t kStaticPartialFloats = size_t(4) << 20;  // 16 MiB of f32 partials per GPU
 static __device__ __align__(256) float g_static_partials[kStaticPartialFloats];
 static __device__ int g_static_status;  // wait-gave-up code of the current call, 0 = fine
+static __device__ int g_static_sticky;  // first such code since the host last looked (lq_check_device_status)
 
 // Second stage for the static array: device code names the array directly.  Sums the splits
 // in a fixed order; if the first stage recorded a timed-out wait, the output is NaN instead.
@@ -1659,28 +1665,44 @@ __global__ void __launch_bounds__(256) reduce_static_kernel(long long split_stri
     int j = (int)(idx - i * J);
     float v = 0.f;
     for (int z = 0; z < splits; ++z) v += g_static_partials[z * split_stride + i * ldp + j];
-    if (g_static_status != 0) v = __int_as_float(0x7FC00000);
+    if (g_static_status != 0) {
+        v = __int_as_float(0x7FC00000);
+        if (idx == 0) atomicCAS(&g_static_sticky, 0, g_static_status);  // survives the next call's reset
+    }
     out[i * ldo + j] = v;
 }
 
 struct StaticCtx {
     float* partials = nullptr;  // device address of g_static_partials on this device
     int* status = nullptr;      // device address of g_static_status on this device
+    int* sticky = nullptr;      // device address of g_static_sticky on this device
     int sm_count = 0;
     bool ready = false;
 };
 
 // One-time set-up per device, with that device current.  In host code the array's name is
 // only a handle; cudaGetSymbolAddress turns it into the pointer a kernel can be given.
+std::mutex g_static_mu;
+StaticCtx g_static_ctx[kMaxDevices];  // fixed storage: a reference handed out stays valid
+
+// Device address of the sticky error word if the static path was set up on `dev`, else NULL.
+int* static_ctx_peek(int dev) {
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    return g_static_ctx[dev].ready ? g_static_ctx[dev].sticky : nullptr;
+}
+
 StaticCtx& static_ctx(int dev) {
-    static std::mutex mu;
-    static std::vector<StaticCtx> ctx;
-    std::lock_guard<std::mutex> lk(mu);
-    if ((int)ctx.size() <= dev) ctx.resize(dev + 1);
-    StaticCtx& c = ctx[dev];
+    if (dev < 0 || dev >= kMaxDevices) throw LqError(LQ_ERR_INVALID, "device index out of range");
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    StaticCtx& c = g_static_ctx[dev];
     if (!c.ready) {
+        int major = 0;
+        LQ_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        if (major != 10)
+            throw LqError(LQ_ERR_UNSUPPORTED, "lq_gemm_bf16_splitk_static needs an sm_100 device (no fallback)");
         LQ_CUDA(cudaGetSymbolAddress((void**)&c.partials, g_static_partials));
         LQ_CUDA(cudaGetSymbolAddress((void**)&c.status, g_static_status));
+        LQ_CUDA(cudaGetSymbolAddress((void**)&c.sticky, g_static_sticky));
         LQ_CUDA(cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev));
         c.ready = true;
     }
@@ -1721,6 +1743,23 @@ void launch_static_split(const void* A, int64_t lda, const void* B, int64_t ldb,
 
 }  // namespace
 
+// Reads and clears the sticky error word of the static path on `device` (0 when that path was never
+// set up there).  The caller has synchronised the stream.
+int lq_static_read_sticky(int device) {
+    if (device < 0 || device >= kMaxDevices) return 0;
+    int* addr = nullptr;
+    {
+        int cur = -1;
+        if (cudaGetDevice(&cur) != cudaSuccess || cur != device) return 0;  // set-up happens with the device current
+        addr = static_ctx_peek(device);
+    }
+    if (!addr) return 0;
+    int v = 0;
+    LQ_CUDA(cudaMemcpy(&v, addr, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v != 0) LQ_CUDA(cudaMemset(addr, 0, sizeof(int)));
+    return v;
+}
+
 extern "C" int lq_gemm_bf16_splitk_static(const void* A, const void* B, int operands_mn, int64_t lda, int64_t ldb,
                                           float* Cout, int64_t ldc, int64_t Mg, int64_t Ng, int64_t Kg, int splits,
                                           void* stream) {
@@ -1728,6 +1767,10 @@ extern "C" int lq_gemm_bf16_splitk_static(const void* A, const void* B, int oper
         LQ_CHECK_ARG(A && B && Cout, "NULL operand");
         LQ_CHECK_ARG(Mg > 0 && Ng > 0 && Kg > 0, "gemm dims must be positive");
         LQ_CHECK_ARG(Ng % 8 == 0 && ldc >= Ng, "Ng must be a multiple of 8 and ldc >= Ng");
+        if (operands_mn)
+            LQ_CHECK_ARG(lda >= Mg && ldb >= Ng, "MN-major operands: lda >= Mg and ldb >= Ng (row strides of [Kg, rows])");
+        else
+            LQ_CHECK_ARG(lda >= Kg && ldb >= Kg, "K-major operands: lda >= Kg and ldb >= Kg (row strides of [rows, Kg])");
         const int64_t kb = (Kg + BK - 1) / BK;
         LQ_CHECK_ARG(splits >= 1 && splits <= 64 && splits <= kb, "splits must be in [1, min(64, ceil(Kg / 64))]");
         const int64_t ldp = ((Ng + 63) / 64) * 64;

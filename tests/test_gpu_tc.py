@@ -176,3 +176,18 @@ def test_bf16_autograd_module():
     assert x.grad is not None and x.grad.shape == x.shape
     assert torch.isfinite(mod.lora_a.grad).all() and float(mod.lora_a.grad.abs().max()) > 0
     assert torch.isfinite(mod.lora_b.grad).all() and float(mod.lora_b.grad.abs().max()) > 0
+
+
+def test_split_gemm_rejects_more_splits_than_k_blocks():
+    """A k-range without a k-block would publish an accumulator that no MMA wrote."""
+    from loractl_b200 import _lib as L
+
+    a = torch.zeros((128, 64), dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros((64, 64), dtype=torch.bfloat16, device="cuda")
+    c = torch.zeros((128, 64), dtype=torch.float32, device="cuda")
+    part = torch.zeros(2 * 128 * 64, dtype=torch.float32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    rc = L.lib().lq_gemm_bf16(a.data_ptr(), 0, 64, b.data_ptr(), 0, 64, c.data_ptr(), L.LQ_F32, 64, 128, 64, 64, 64, 2,
+                              part.data_ptr(), None, st)
+    assert rc == L.LQ_ERR_INVALID
+    assert b"splits must not exceed" in L.lib().lq_last_error()

@@ -52,6 +52,8 @@ def test_static_scratch_matches_workspace_path_on_two_calls_in_a_row():
         (520, 128, 640, False, 3),   # smaller, different data: stale partials must not leak in
         (384, 64, 1000, True, 5),
         (1000, 64, 1024, False, 4),  # the first problem again, after the array was reused
+        (4100, 128, 512, False, 2),  # many row tiles, two column tiles: the tile raster of the first stage
+        (300, 72, 448, False, 3),    # Ng not a multiple of 64: the partial rows are wider than C's
     ]
     first = None
     for i, (mg, ng, kg, mn, splits) in enumerate(cases):
@@ -70,6 +72,43 @@ def test_static_scratch_matches_workspace_path_on_two_calls_in_a_row():
             first = got.clone()
         if i == 3:
             assert torch.equal(got, first)  # deterministic: fixed split ranges, fixed reduction order
+
+
+def test_static_scratch_call_allocates_no_device_memory():
+    """After the one-time set-up call, a call must leave the device's free memory untouched."""
+    from loractl_b200 import _lib as L
+
+    a = dev(seeded((512, 768), 3), torch.bfloat16)
+    b = dev(seeded((64, 768), 4), torch.bfloat16)
+    rc, _ = _static(a, b, False, 4)  # set-up call (symbol address look-up, kernel attributes)
+    assert rc == L.LQ_OK, L.lib().lq_last_error()
+    torch.cuda.synchronize()
+    c = torch.empty((512, 64), dtype=torch.float32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    free_before, _ = torch.cuda.mem_get_info()
+    launches_before = L.lib().lq_kernel_launch_count()
+    for _ in range(3):
+        rc = L.lib().lq_gemm_bf16_splitk_static(a.data_ptr(), b.data_ptr(), 0, a.stride(0), b.stride(0),
+                                                c.data_ptr(), 64, 512, 64, 768, 4, st)
+        assert rc == L.LQ_OK, L.lib().lq_last_error()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, "the allocation-free entry changed the device's free memory"
+    assert L.lib().lq_kernel_launch_count() - launches_before == 6  # two kernels per call, nothing else
+    assert reldev(host(c), host(a.float() @ b.float().t())) <= 1e-5
+    L.check(L.lib().lq_check_device_status(st))  # no bounded wait gave up
+
+
+def test_static_scratch_rejects_short_row_strides():
+    from loractl_b200 import _lib as L
+
+    a = torch.zeros((256, 512), dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros((64, 512), dtype=torch.bfloat16, device="cuda")
+    c = torch.zeros((256, 64), dtype=torch.float32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    rc = L.lib().lq_gemm_bf16_splitk_static(a.data_ptr(), b.data_ptr(), 0, 256, 512, c.data_ptr(), 64, 256, 64, 512,
+                                            2, st)
+    assert rc == L.LQ_ERR_INVALID  # lda < Kg
 
 
 def test_static_scratch_limit_is_enforced_by_name():
