@@ -270,6 +270,20 @@ int lq_profile_kinds(void);
 const char* lq_profile_kind_name(int kind);
 int lq_profile_collect(double* ms_by_kind, uint64_t* launches_by_kind, int n_kinds);
 
+/* Run-time switches of the kernel selection, for A/B measurements and tests (the reference selects
+ * code paths through `compute.*` config keys, crates/loractl-core/src/config.rs:704-760; these are
+ * the equivalent knobs below the boundary).  Process-wide; initial values come from the environment
+ * variables of the same meaning (LQ_W4, LQ_W4_EXACT).
+ *   "w4"        1 (default): int4 weights at >= 128 tokens are dequantised inside the GEMM mainloop
+ *               and no bf16 copy of the weight is written to HBM; 0: dequantise into the workspace.
+ *   "w4_exact"  how the in-mainloop conversion forms a bf16 weight from (q, scale):
+ *               1: bf16(q * scale) with the f32 product, bit-identical to the workspace path;
+ *               2: fma(q, s_hi, bf16(q * s_lo)) with the scale split into two bf16 terms — one
+ *                  rounding of q * scale except within 2^-18 of a rounding boundary;
+ *               0: bf16(q * bf16(scale)).
+ * Unknown names are LQ_ERR_INVALID. */
+int lq_option_set(const char* name, int value);
+
 /* The bare tcgen05 contraction the hot path is built from, exposed for unit tests and
  * roofline probes: C[Mg, Ng] = A . B^T + bias with bf16 operands and f32 accumulation.
  * An operand is K-major ([rows, Kg], Kg contiguous; *_mn = 0) or MN-major ([Kg, rows], rows

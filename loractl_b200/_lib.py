@@ -69,6 +69,7 @@ SIGNATURES = {
     "lq_profile_kind_name": (C.c_char_p, [_I]),
     "lq_profile_collect": (_I, [C.POINTER(C.c_double), C.POINTER(C.c_uint64), _I]),
     "lq_gemm_bf16_splitk_static": (_I, [_P, _P, _I, _I64, _I64, _P, _I64, _I64, _I64, _I64, _I, _P]),
+    "lq_option_set": (_I, [C.c_char_p, _I]),
     "lq_gemm_bf16": (_I, [_P, _I, _I64, _P, _I, _I64, _P, _I, _I64, _I64, _I64, _I64, _I, _I, _P, _P, _P]),
 }
 

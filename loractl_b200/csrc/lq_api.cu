@@ -506,6 +506,14 @@ int lq_selftest_bounded_wait(unsigned limit_ms, void* stream) {
     });
 }
 
+int lq_option_set(const char* name, int value) {
+    return guarded([&] {
+        LQ_CHECK_ARG(name != nullptr, "option name is NULL");
+        if (!lq_w4_option_set(name, value))
+            throw LqError(LQ_ERR_INVALID, std::string("unknown option '") + name + "' (known: w4, w4_exact)");
+    });
+}
+
 int lq_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, int64_t ldb, void* C, int c_dtype,
                  int64_t ldc, int64_t Mg, int64_t Ng, int64_t Kg, int block_n, int splits, float* partial_ws,
                  const float* bias, void* stream) {

@@ -1,0 +1,55 @@
+// Pieces shared by the tcgen05 GEMM translation units: tile constants, the kernel parameter block
+// and the raster that maps a work item to its output tile.
+#pragma once
+
+#include <stdint.h>
+
+namespace lqgemm {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+
+struct GemmParams {
+    int Mg = 0, Ng = 0;
+    int kb0 = 0, kb1 = 0;
+    int m_tiles = 0, n_tiles = 0, splits = 1;
+    void* C = nullptr;
+    long long ldc = 0, split_stride = 0;
+    const float* bias = nullptr;
+    int* status = nullptr;
+    // optional epilogue scales: v = acc * row_scale[row] * col_scale[col] (NULL = 1); with
+    // col_scale_bcast the single value col_scale[0] applies to every column
+    const float* row_scale = nullptr;
+    const float* col_scale = nullptr;
+    int col_scale_bcast = 0;
+    int tma_store = 0;  // bf16 output leaves through shared memory and TMA tensor stores (full 64-byte row pieces)
+    int group_m = 0;    // m-tiles per raster group (0 = 16)
+};
+
+template <int BLOCK_N>
+struct Cfg {
+    static constexpr uint32_t A_BYTES = BM * BK * 2;
+    static constexpr uint32_t B_BYTES = BLOCK_N * BK * 2;
+    static constexpr int STAGES = (208 * 1024) / (A_BYTES + B_BYTES);
+    // 2 accumulator stages; the allocation must be a power of two >= 32 columns
+    static constexpr uint32_t TMEM_COLS = BLOCK_N * 2 <= 128 ? 128 : (BLOCK_N * 2 <= 256 ? 256 : 512);
+    static constexpr uint32_t STAGE_OUT = 8 * 2048;  // per epilogue warp: 32 rows x 64 bytes of bf16 output
+    static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + STAGE_OUT + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void item_coords(const GemmParams& p, int item, int& m_tile, int& n_tile, int& z) {
+    const int tiles = p.m_tiles * p.n_tiles;
+    z = item / tiles;
+    int t = item - z * tiles;
+    const int GROUP = p.group_m > 0 ? p.group_m : 16;  // m-tiles per raster group: a band of A kept hot in L2
+    int per_group = GROUP * p.n_tiles;
+    int g = t / per_group;
+    int first_m = g * GROUP;
+    int gsize = min(GROUP, p.m_tiles - first_m);
+    int r = t - g * per_group;
+    m_tile = first_m + r % gsize;
+    n_tile = r / gsize;
+}
+
+
+}  // namespace lqgemm

@@ -26,6 +26,7 @@
 
 #include <cuda_fp8.h>
 
+#include "lq_gemm.cuh"
 #include "lq_prof.cuh"
 #include "lq_tc.cuh"
 #include "lq_umma.cuh"
@@ -34,51 +35,9 @@ namespace {
 
 using namespace umma;
 
-constexpr int BM = 128;
-constexpr int BK = 64;
+using namespace lqgemm;
+
 constexpr int kThreads = 320;  // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quarter)
-
-struct GemmParams {
-    int Mg = 0, Ng = 0;
-    int kb0 = 0, kb1 = 0;
-    int m_tiles = 0, n_tiles = 0, splits = 1;
-    void* C = nullptr;
-    long long ldc = 0, split_stride = 0;
-    const float* bias = nullptr;
-    int* status = nullptr;
-    // optional epilogue scales: v = acc * row_scale[row] * col_scale[col] (NULL = 1); with
-    // col_scale_bcast the single value col_scale[0] applies to every column
-    const float* row_scale = nullptr;
-    const float* col_scale = nullptr;
-    int col_scale_bcast = 0;
-    int tma_store = 0;  // bf16 output leaves through shared memory and TMA tensor stores (full 64-byte row pieces)
-    int group_m = 0;    // m-tiles per raster group (0 = 16)
-};
-
-template <int BLOCK_N>
-struct Cfg {
-    static constexpr uint32_t A_BYTES = BM * BK * 2;
-    static constexpr uint32_t B_BYTES = BLOCK_N * BK * 2;
-    static constexpr int STAGES = (208 * 1024) / (A_BYTES + B_BYTES);
-    // 2 accumulator stages; the allocation must be a power of two >= 32 columns
-    static constexpr uint32_t TMEM_COLS = BLOCK_N * 2 <= 128 ? 128 : (BLOCK_N * 2 <= 256 ? 256 : 512);
-    static constexpr uint32_t STAGE_OUT = 8 * 2048;  // per epilogue warp: 32 rows x 64 bytes of bf16 output
-    static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + STAGE_OUT + 1024 /*align*/ + 256 /*barriers*/;
-};
-
-__device__ __forceinline__ void item_coords(const GemmParams& p, int item, int& m_tile, int& n_tile, int& z) {
-    const int tiles = p.m_tiles * p.n_tiles;
-    z = item / tiles;
-    int t = item - z * tiles;
-    const int GROUP = p.group_m > 0 ? p.group_m : 16;  // m-tiles per raster group: a band of A kept hot in L2
-    int per_group = GROUP * p.n_tiles;
-    int g = t / per_group;
-    int first_m = g * GROUP;
-    int gsize = min(GROUP, p.m_tiles - first_m);
-    int r = t - g * per_group;
-    m_tile = first_m + r % gsize;
-    n_tile = r / gsize;
-}
 
 template <typename OutT>
 __device__ __forceinline__ void store8(OutT* dst, const float* v);
@@ -887,21 +846,7 @@ void launch_gemm_pair(const Operand& a0, const Operand& b0, int64_t K0, const Op
     p.tma_store = 1;
     CUtensorMap tC = make_store_map(Cout, Ng, Mg, ldc);
     const long long items = (long long)p.m_tiles * p.n_tiles;
-    {
-        // Raster: the CTAs of a wave run through K in step, so a wave reads each of its distinct A and
-        // B row bands from DRAM once.  With 16-pair-tile groups a wave is 16 bands of A and ncl/16 of B;
-        // when that exceeds what L2 keeps comfortably (long K) and the whole B operand is small enough
-        // to stay resident, waves instead span ALL column tiles of a few A bands: B is then read from
-        // DRAM once for the whole launch and A streams through.
-        const int ncl_est = std::max(1, ctx.sm_count / 2);
-        const double esz = F8 ? 1.0 : 2.0;
-        const double wave16 = (16.0 * 256 + (double)ncl_est / 16 * BLOCK_N) * (double)K0 * esz;
-        const double whole_b = (double)Ng * (double)K0 * esz;
-        p.group_m = 16;
-        if (wave16 > 48e6 && whole_b <= 90e6) p.group_m = std::max(1, (ncl_est + p.n_tiles - 1) / p.n_tiles);
-        static const int forced = [] { const char* e = getenv("LQ_GROUP_M"); return e ? atoi(e) : 0; }();
-        if (forced > 0) p.group_m = forced;
-    }
+    p.group_m = lq_tc_pair_group_m(ctx.sm_count, BLOCK_N, Ng, K0, F8 ? 1 : 2, p.n_tiles);
     auto kern = umma_gemm2_kernel<BLOCK_N, F8>;
     LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
     // persistent grid = the number of CTA pairs that can be resident at once (asked once per device)
@@ -1324,6 +1269,25 @@ const uint8_t* ensure_transposed(const lq_weight* w, cudaStream_t st) {
 
 }  // namespace
 
+// Raster of the CTA-pair GEMMs: the CTAs of a wave run through K in step, so a wave reads each of its
+// distinct A and B row bands from DRAM once.  With 16-pair-tile groups a wave is 16 bands of A and
+// ncl/16 of B; when that exceeds what L2 keeps comfortably (long K) and the whole B operand is small
+// enough to stay resident, waves instead span ALL column tiles of a few A bands: B is then read from
+// DRAM once for the whole launch and A streams through.
+int lq_tc_pair_group_m(int sm_count, int block_n, int64_t Ng, int64_t K0, int b_elem_bytes, int n_tiles) {
+    const int ncl_est = std::max(1, sm_count / 2);
+    const double esz = (double)b_elem_bytes;
+    const double wave16 = (16.0 * 256 + (double)ncl_est / 16 * block_n) * (double)K0 * esz;
+    const double whole_b = (double)Ng * (double)K0 * esz;
+    int group_m = 16;
+    if (wave16 > 48e6 && whole_b <= 90e6) group_m = std::max(1, (ncl_est + n_tiles - 1) / n_tiles);
+    static const int forced = [] { const char* e = getenv("LQ_GROUP_M"); return e ? atoi(e) : 0; }();
+    if (forced > 0) group_m = forced;
+    return group_m;
+}
+CUtensorMap lq_tc_make_store_map(const void* base, int64_t cols, int64_t rows, int64_t ld) {
+    return make_store_map(base, cols, rows, ld);
+}
 CUtensorMap lq_tc_make_map(const void* base, int64_t inner, int64_t rows, int64_t ld, int box_rows) {
     return make_map(base, inner, rows, ld, box_rows);
 }
@@ -1376,7 +1340,14 @@ void lq_tc_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, con
         throw LqError(LQ_ERR_WORKSPACE, "workspace too small: need " + std::to_string(t.bytes) + " bytes, got " +
                                             std::to_string(ws_bytes));
     Operand a0{X, false, K}, b0{t.wscr, false, K};
+    // int4 weights at tile-filling sizes: the weight is converted inside the GEMM's mainloop and no
+    // bf16 copy of it is written; otherwise it is dequantised once per call into the scratch
+    const bool w4 = lq_w4_supported(w, N, 0);
     if (r == 0) {
+        if (w4) {
+            lq_w4_gemm(w, 0, X, K, nullptr, 0, nullptr, 0, 0, Y, M, N, w->bias, st);
+            return;
+        }
         lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, st);
         main_gemm<__nv_bfloat16>(a0, b0, K, nullptr, nullptr, 0, (__nv_bfloat16*)Y, M, N, M, w->bias, ctx.sm_count, st);
         return;
@@ -1386,7 +1357,7 @@ void lq_tc_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, con
     fj.fork();
     // side: frozen weight -> bf16 scratch [M, K] (rounds q*scale, resp. LUT*scale, once to bf16),
     //       and B^T [M, EXT] for the K extension
-    lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, fj.side());
+    if (!w4) lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, fj.side());
     cast_pad(B, 1, M, t.pext, EXT, M, r, EXT, 1.f, fj.side());
     // main: H = X . A  (f32 [N, r] for the backward; bf16 s*H, zero padded, as the K extension)
     cast_pad(A, 1, r, t.pdown, K, r, (int)K, (int)K, 1.f, st);  // A^T [r, K]
@@ -1394,6 +1365,10 @@ void lq_tc_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, con
     skinny_down(X, N, K, K, t.pdown, K, r, 1.f, Hf, t.ext_a, s, t.part, ctx.sm_count, st);
     fj.join(0);
     // Y = [X | s*H] . [W | B^T]^T + bias
+    if (w4) {
+        lq_w4_gemm(w, 0, X, K, t.ext_a, EXT, t.pext, EXT, EXT, Y, M, N, w->bias, st);
+        return;
+    }
     Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
     main_gemm<__nv_bfloat16>(a0, b0, K, &a1, &b1, EXT, (__nv_bfloat16*)Y, M, N, M, w->bias, ctx.sm_count, st);
 }
@@ -1411,8 +1386,11 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
                                             std::to_string(ws_bytes));
     const int EXT = ext_width(r > 0 ? r : 1);
     Operand a0{dY, false, M}, b0{t.wscr, false, M};
+    const bool w4 = dX && lq_w4_supported(w, N, 1);
     if (r == 0) {
-        if (dX) {
+        if (dX && w4) {
+            lq_w4_gemm(w, 1, dY, M, nullptr, 0, nullptr, 0, 0, dX, K, N, nullptr, st);
+        } else if (dX) {
             lq_launch_dequant(w, t.wscr, LQ_BF16, M, 1, st);  // W^T [K, M]
             main_gemm<__nv_bfloat16>(a0, b0, M, nullptr, nullptr, 0, (__nv_bfloat16*)dX, K, N, K, nullptr, ctx.sm_count, st);
         }
@@ -1422,7 +1400,7 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
     fj.fork();
     // side: what the dX GEMM needs besides dH: W^T [K, M] and A [K, EXT] in bf16
     if (dX) {
-        lq_launch_dequant(w, t.wscr, LQ_BF16, M, 1, fj.side());
+        if (!w4) lq_launch_dequant(w, t.wscr, LQ_BF16, M, 1, fj.side());
         cast_pad(A, r, 1, t.pext, EXT, K, r, EXT, 1.f, fj.side());
     }
     fj.record(0);  // the caller's stream waits for this point just before the dX GEMM
@@ -1442,8 +1420,12 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
     skinny_down(dY, N, M, M, t.pdown, M, r, s, t.dHf, t.ext_a, 1.f, t.part, ctx.sm_count, st);
     if (dX) {  // dX = [dY | dH] . [W^T | A]^T
         fj.wait(0);
-        Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
-        main_gemm<__nv_bfloat16>(a0, b0, M, &a1, &b1, EXT, (__nv_bfloat16*)dX, K, N, K, nullptr, ctx.sm_count, st);
+        if (w4) {
+            lq_w4_gemm(w, 1, dY, M, t.ext_a, EXT, t.pext, EXT, EXT, dX, K, N, nullptr, st);
+        } else {
+            Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
+            main_gemm<__nv_bfloat16>(a0, b0, M, &a1, &b1, EXT, (__nv_bfloat16*)dX, K, N, K, nullptr, ctx.sm_count, st);
+        }
     }
     if (dA)  // dA[K, r] = X^T . dH
         skinny_grad(X, N, K, K, t.ext_a, r, 1.f, dA, 0, accumulate, t.part, ctx.sm_count, st);

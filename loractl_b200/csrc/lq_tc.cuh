@@ -33,6 +33,10 @@ void lq_tc_selftest_wait(int device, unsigned limit_ms, cudaStream_t st);
 CUtensorMap lq_tc_make_map(const void* base, int64_t inner, int64_t rows, int64_t ld, int box_rows);
 // Same for a byte matrix: box 128 bytes x box_rows, 128-byte swizzle.
 CUtensorMap lq_tc_make_map_u8(const void* base, int64_t inner, int64_t rows, int64_t ld, int box_rows);
+// bf16 output [rows, cols]: box 32 x 32, 64-byte swizzle, for the epilogues' TMA tensor stores.
+CUtensorMap lq_tc_make_store_map(const void* base, int64_t cols, int64_t rows, int64_t ld);
+// m-tiles per raster group of a CTA-pair GEMM (see the definition for the rule).
+int lq_tc_pair_group_m(int sm_count, int block_n, int64_t Ng, int64_t K0, int b_elem_bytes, int n_tiles);
 int* lq_tc_status_word(int device);
 // Event fork / join with the per-(device, caller stream) side stream: `fork` returns the stream to
 // enqueue independent work on (the caller's own stream when forking is switched off); `join` makes
@@ -59,3 +63,12 @@ void lq_w8a8_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, c
 void lq_w8a8_bwd(const lq_weight* w, const void* dY, const void* X, const float* H, int64_t N, const float* A,
                  const float* B, int r, float s, void* dX, float* dA, float* dB, int accumulate, void* ws,
                  size_t ws_bytes, cudaStream_t st);
+
+// Frozen GEMM with the int4 weight dequantised inside the mainloop (lq_w4.cu): no bf16 copy of the
+// weight exists in HBM.  `transposed` = 0: C[Mg, d_out] = A0[Mg, d_in] . W^T (+ bias); 1: C[Mg, d_in] =
+// A0[Mg, d_out] . W.  (a1, b1): optional bf16 K extension [Mg, K1] / [Ng, K1] (the LoRA product).
+bool lq_w4_supported(const lq_weight* w, int64_t Mg, int transposed);
+bool lq_w4_option_set(const char* name, int value);  // "w4", "w4_exact"; false: unknown name
+void lq_w4_gemm(const lq_weight* w, int transposed, const void* A0, int64_t lda, const void* a1, int64_t lda1,
+                const void* b1, int64_t ldb1, int64_t K1, void* Cout, int64_t ldc, int64_t Mg, const float* bias,
+                cudaStream_t st);

@@ -132,11 +132,48 @@ def fp8_encode() -> None:
     print("wrote fp8_encode_golden.json")
 
 
+def mmdit_block0(ref: pathlib.Path) -> None:
+    """Block 0 of the reference's tiny MMDiT trace, cut out of its golden: the stage tensors either
+    side of the first trunk block (crates/loractl-core/tests/fixtures/mmdit_tiny_golden.json:
+    after_first, after_txtmlp, tvec, pos, txtmask -> after_block0) and that block's tensors from
+    tests/fixtures/tiny-mmdit/model.safetensors, as one small safetensors file (values unchanged,
+    stored as f32)."""
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+
+    fx = ref / "crates" / "loractl-core" / "tests" / "fixtures"
+    g = json.loads((fx / "mmdit_tiny_golden.json").read_text())
+    out = {}
+    for name in ("after_first", "after_txtmlp", "tvec", "pos", "after_block0"):
+        out[f"stage.{name}"] = torch.tensor(g[name], dtype=torch.float64).reshape(g[f"{name}_shape"]).to(torch.float32)
+    out["stage.txtmask"] = torch.tensor(g["txtmask"], dtype=torch.float32)
+    with safe_open(str(fx / "tiny-mmdit" / "model.safetensors"), "pt") as f:
+        for k in f.keys():
+            if k.startswith("blocks.0."):
+                out[k] = f.get_tensor(k).to(torch.float32).contiguous()
+    cfg = {k: str(g["config"][k]) for k in ("features", "heads", "kvheads", "multiplier")}
+    save_file(out, str(HERE / "mmdit_tiny_block0.safetensors"), metadata=cfg)
+    print("wrote mmdit_tiny_block0.safetensors", len(out), "tensors")
+
+
+def gpt2_tiny(ref: pathlib.Path) -> None:
+    """Pass-through of the reference's tiny GPT-2 fixture (weights and golden logits,
+    crates/loractl-core/tests/fixtures/gpt2_tiny_golden.json, tiny-gpt2/model.safetensors)."""
+    import shutil
+
+    fx = ref / "crates" / "loractl-core" / "tests" / "fixtures"
+    (HERE / "gpt2_tiny_golden.json").write_text(json.dumps(json.loads((fx / "gpt2_tiny_golden.json").read_text())))
+    shutil.copyfile(fx / "tiny-gpt2" / "model.safetensors", HERE / "gpt2_tiny.safetensors")
+    print("copied gpt2 tiny fixture")
+
+
 def main() -> None:
     if len(sys.argv) != 2:
         raise SystemExit("usage: make_golden.py <path to the loractl checkout>")
     ref = pathlib.Path(sys.argv[1])
     passthrough(ref)
+    mmdit_block0(ref)
+    gpt2_tiny(ref)
     lora_toy_inputs(ref)
     quant_extra(ref)
     fp8_encode()
