@@ -63,23 +63,26 @@ def main_gemm_flops(n, k, m, r):
 # ---------------------------------------------------------------------------------------------
 # CPU restatement of the reference's op sequence (the `cpu_baseline` / `--impl reference` leg)
 # ---------------------------------------------------------------------------------------------
-def cpu_reference_rate(workload: str, sample_tokens: int, reps: int, seed: int = 5):
-    """Times fwd+bwd of the reference's sequence in numpy f32 on all host cores.
-    Returns (tflops, seconds_per_step, cores)."""
+_CPU_WEIGHTS: dict = {}
+
+
+def cpu_reference_rate(workload: str, sample_tokens: int, reps: int, seed: int = 5, threads: int = 0):
+    """Times fwd+bwd of the reference's sequence in numpy f32 on `threads` BLAS threads (0 = all host
+    cores; 1 = what the reference's ndarray backend resolves to, matrixmultiply without threading).
+    Returns (tflops, seconds_per_step, threads used)."""
     import numpy as np
 
     from oracle import lq_oracle as O
 
     scheme, k, m, r, alpha, _, group = WORKLOADS[workload]
     rng = np.random.default_rng(seed)
-    w = (rng.standard_normal((m, k), dtype=np.float32) * np.float32(0.02))
-    if scheme == "fp8":
-        wb, sc = O.fp8_quantize(w, per_channel=True)
-        dequant = lambda: O.fp8_dequant(wb, sc)
-    else:
-        codes, scales = O.quantize(w, group, 4)
-        dequant = lambda: O.dequantize(codes, scales, group)
-    del w
+    if (workload, seed) not in _CPU_WEIGHTS:  # quantizing 38 M weights in numpy takes longer than the timed steps
+        w = (rng.standard_normal((m, k), dtype=np.float32) * np.float32(0.02))
+        _CPU_WEIGHTS[(workload, seed)] = O.fp8_quantize(w, per_channel=True) if scheme == "fp8" else O.quantize(w, group, 4)
+        del w
+    q0, q1 = _CPU_WEIGHTS[(workload, seed)]
+    dequant = (lambda: O.fp8_dequant(q0, q1)) if scheme == "fp8" else (lambda: O.dequantize(q0, q1, group))
+    rng = np.random.default_rng(seed + 1)
     n = sample_tokens
     x = rng.standard_normal((n, k), dtype=np.float32)
     dy = rng.standard_normal((n, m), dtype=np.float32)
@@ -94,12 +97,14 @@ def cpu_reference_rate(workload: str, sample_tokens: int, reps: int, seed: int =
 
     # torchrun exports OMP_NUM_THREADS=1; the baseline is defined on all host cores, so size the
     # BLAS pool explicitly and report the thread count actually used
-    cores = len(os.sched_getaffinity(0))
+    cores = threads if threads > 0 else len(os.sched_getaffinity(0))
     try:
         from threadpoolctl import threadpool_limits
         limiter = threadpool_limits(limits=cores)
     except Exception:
         limiter = None
+        if threads == 1:
+            raise
     try:
         one_step()
         t0 = time.perf_counter()
@@ -113,23 +118,35 @@ def cpu_reference_rate(workload: str, sample_tokens: int, reps: int, seed: int =
 
 
 def run_reference(args):
+    """`--impl reference`: the reference's op sequence on the host cores (numpy port of the oracle), on
+    the bench's own workload at its full token count, all host threads; beside it the single-threaded
+    rate (what burn-ndarray's matrixmultiply resolves to) and the config-1 figures."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     wl = args.workload
     scheme, k, m, r, alpha, tokens, group = WORKLOADS[wl]
-    sample = min(tokens, 1024)
-    reps = max(1, args.steps)
+    reps = max(1, min(args.steps, 3))
     # warm-up counted inside cpu_reference_rate (one untimed step); extra warm-ups are pointless on CPU
-    tf, dt, cores = cpu_reference_rate(wl, sample, min(reps, 5))
+    tf, dt, cores = cpu_reference_rate(wl, tokens, reps)
+    tf1, dt1, _ = cpu_reference_rate(wl, min(tokens, 256), 1, threads=1)
+    c1 = WORKLOADS["cfg1"]
+    c1_all, c1_dt, _ = cpu_reference_rate("cfg1", c1[5], 2)
+    c1_one, c1_dt1, _ = cpu_reference_rate("cfg1", min(c1[5], 512), 1, threads=1)
     line = {
         "impl": "reference", "metric": METRIC, "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": min(reps, 5), "warmup": 1, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "steps": reps, "warmup": 1, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": wl, "scheme": scheme, "d_in": k, "d_out": m, "rank": r, "tokens": sample,
-                   "sample": f"{sample} of {tokens} tokens per step"},
+        "config": {"workload": wl, "scheme": scheme, "d_in": k, "d_out": m, "rank": r, "alpha": alpha,
+                   "tokens_per_gpu": tokens, "parallelism": "host cores"},
         "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                         "sample": f"fwd+bwd on {sample} of {tokens} tokens, numpy f32 (BLAS threads = host cores)"},
+                         "sample": f"fwd+bwd on all {tokens} tokens, {reps} reps, numpy f32 (BLAS threads = host cores)"},
+        "cpu_single_thread": {"value": tf1, "unit": "TFLOP/s", "cores": 1, "ms_per_step": dt1 * 1e3,
+                              "sample": f"fwd+bwd on {min(tokens, 256)} of {tokens} tokens, 1 rep, 1 BLAS thread"},
+        "cpu_cfg1": {"all_cores": {"value": c1_all, "unit": "TFLOP/s", "cores": cores, "ms_per_step": c1_dt * 1e3,
+                                   "sample": f"int4 3072x3072 rank 16, all {c1[5]} tokens, f32"},
+                     "single_thread": {"value": c1_one, "unit": "TFLOP/s", "cores": 1, "ms_per_step": c1_dt1 * 1e3,
+                                       "sample": f"int4 3072x3072 rank 16, {min(c1[5], 512)} of {c1[5]} tokens, f32"}},
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -139,6 +156,113 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    return json.loads(p.read_text()) if p.exists() else {}
+
+
+def measure_fp8_peak(dev):
+    """No fp8 peak is in MEASURED_PEAKS.json: measure one here the way the bf16 one was measured
+    (library GEMM, 8192^3, best of 13 single launches, CUDA events) and use it as the denominator
+    of the native-fp8 fractions."""
+    import torch
+
+    a8 = torch.randn(8192, 8192, device=dev).to(torch.float8_e4m3fn)
+    b8 = torch.randn(8192, 8192, device=dev).to(torch.float8_e4m3fn).t()
+    one = torch.ones((), device=dev)
+    best = 1e9
+    for _ in range(13):
+        q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        q0.record()
+        torch._scaled_mm(a8, b8, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        q1.record()
+        torch.cuda.synchronize()
+        best = min(best, q0.elapsed_time(q1))
+    return 2 * 8192 ** 3 / (best * 1e-3) / 1e12
+
+
+def measure_linear_quick(dev, wl: str, steps: int, rank_seed: int = 0):
+    """One single-linear workload (fwd + bwd, inputs resident, CUDA graph replay): median of five
+    regions of `steps` replays, per-kernel-class times from an eager pass, frozen-GEMM fraction of
+    the measured bf16 burst peak."""
+    import torch
+
+    import loractl_b200 as lb
+    from loractl_b200 import _lib as L
+    from loractl_b200 import quant as Q
+
+    lib = L.lib()
+    scheme, k, m, r, alpha, n, group = WORKLOADS[wl]
+    s_ = alpha / r
+    g = torch.Generator(device=dev).manual_seed(5)
+    w = torch.randn((m, k), generator=g, device=dev) * 0.02
+    wq = lb.fp8_quantize(w, per_channel=True) if scheme == "fp8" else lb.quantize_linear_weight(w, 4, group)
+    del w
+    g = torch.Generator(device=dev).manual_seed(7 + rank_seed)
+    a = torch.randn((k, r), generator=g, device=dev) / (k ** 0.5)
+    b = torch.randn((r, m), generator=g, device=dev) * 0.01
+    # inputs and outputs of one step must exceed the 126 MB L2, else consecutive steps would be served
+    # from it: smaller workloads rotate through several input sets (a "step" call runs one of each)
+    footprint = 4 * n * (k + m)
+    n_sets = max(1, -(-int(1.6 * 126e6) // footprint))
+    xs = [torch.randn((n, k), generator=g, device=dev).to(torch.bfloat16) for _ in range(n_sets)]
+    dys = [torch.randn((n, m), generator=g, device=dev).to(torch.bfloat16) for _ in range(n_sets)]
+    da, db = torch.zeros((k, r), device=dev), torch.zeros((r, m), device=dev)
+    mir = Q.lora_mirror(a, b)
+
+    def step():
+        for x, dy in zip(xs, dys):
+            y, h = Q.linear_fwd_raw(wq, x, a, b, s_, mirror=mir)
+            Q.linear_bwd_raw(wq, dy, x, h, a, b, s_, da_out=da, db_out=db, mirror=mir)
+
+    for _ in range(3):
+        step()
+    lb.check_device_status(dev)
+    lib.lq_profile_enable(1)
+    lib.lq_profile_collect(None, None, 0)
+    for _ in range(steps):
+        step()
+    nk = lib.lq_profile_kinds()
+    msk, cnt = (C.c_double * nk)(), (C.c_uint64 * nk)()
+    lib.lq_profile_collect(msk, cnt, nk)
+    lib.lq_profile_enable(0)
+    kinds = {lib.lq_profile_kind_name(i).decode(): (msk[i], int(cnt[i])) for i in range(nk)}
+    gph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        step()
+        with torch.cuda.graph(gph, stream=side):
+            step()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    for _ in range(3):
+        gph.replay()
+    regions = []
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            gph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        regions.append(e0.elapsed_time(e1) / (steps * n_sets))
+    lb.check_device_status(dev)
+    ms = statistics.median(regions)
+    peaks = load_peaks()
+    peak = peaks.get("bf16_tflops", 1590.0)
+    gm_ms, gm_n = kinds.get("gemm_main", (0.0, 0))
+    gemm_tf = (main_gemm_flops(n, k, m, r) / 2) / (gm_ms / max(gm_n, 1) * 1e-3) / 1e12 if gm_n else None
+    fl = step_flops(n, k, m, r)
+    return {
+        "workload": wl, "scheme": scheme, "d_in": k, "d_out": m, "rank": r, "tokens": n, "group": group,
+        "value": fl / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "regions_ms": regions,
+        "frac_of_bf16_burst": fl / (ms * 1e-3) / 1e12 / peak,
+        "gemm_tflops": gemm_tf, "gemm_frac": gemm_tf / peak if gemm_tf else None, "peak": peak,
+        "by_kernel_ms_per_step": {kk: v[0] / (steps * n_sets) for kk, v in kinds.items() if v[1]},
+        "l2": f"{n_sets} rotating input/output sets of {footprint / 1e6:.0f} MB = {n_sets * footprint / 1e6:.0f} MB > 126 MB L2",
+    }
+
 class ClockSampler:
     """Samples nvidia-smi clocks / throttle reasons for one GPU while the timed regions run."""
 
@@ -161,6 +285,17 @@ class ClockSampler:
     def _pump(self):
         for line in self.proc.stdout:
             self.rows.append((time.time(), line.strip()))
+
+    def median_sm_mhz(self, t0, t1):
+        """Median SM clock of the samples taken between two wall-clock times (None without samples)."""
+        vals = []
+        for (t, r) in list(self.rows):
+            if t0 <= t <= t1:
+                try:
+                    vals.append(float(r.split(",")[0]))
+                except ValueError:
+                    pass
+        return statistics.median(vals) if vals else None
 
     def stop(self, t0, t1):
         if self.proc is None:
@@ -310,11 +445,19 @@ def run_ours(args):
 
         for _ in range(3):
             graph_step()
-        total_ms = timed(graph_step, args.steps)
     else:
         graph_step = lambda: step(x, dy)
-        total_ms = timed(graph_step, args.steps)
+    # `value`: the median of five timed regions of K steps each (every region bracketed by a barrier
+    # and a device synchronisation, timed with CUDA events, max over ranks)
+    regions_ms = [timed(graph_step, args.steps) for _ in range(5)]
+    total_ms = statistics.median(regions_ms)
     lb.check_device_status(dev)
+    # `sustained`: one region of at least two seconds, the regime a training loop runs in (the SM clock
+    # settles well below its burst value under the power cap); compared with the sustained cuBLAS peak
+    sus_steps = max(args.steps, int(2000.0 / max(total_ms / args.steps, 1e-3)) + 1)
+    t_sus0 = time.time()
+    sus_ms = timed(graph_step, sus_steps)
+    t_sus1 = time.time()
 
     # Scaled-fp8 workloads: also time the same step with native e4m3 MMA (LQ_BF16_W8A8), reported
     # beside the headline under "native_fp8" (the headline itself stays the bf16-compute path).
@@ -420,7 +563,28 @@ def run_ours(args):
     sync_all()
     e2e_ms = timed(lambda: e2e_loop(e2e_steps), 1)
     t_wall1 = time.time()
+    sus_mhz = sampler.median_sm_mhz(t_sus0, t_sus1) if sampler else None
     clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
+
+    # ---- further keys of the default line: the other workloads of the path, measured in the same run ----
+    extras = {}
+    if not args.no_extras and wl == "cfg2" and not fp8c:
+        # config 1 (int4 block 64, 3072 x 3072, rank 16, 4096 tokens) on this rank's GPU
+        extras["int4_cfg1"] = measure_linear_quick(dev, "cfg1", max(args.steps, 10), rank)
+        extras["int4_cfg3up"] = measure_linear_quick(dev, "cfg3up", max(args.steps, 10), rank)
+        if world == 1:
+            # the packed-weight stream at <= 64 tokens (one GPU; the sites do not shard)
+            sres, hbm_peak = measure_stream(dev, 10)
+            extras["stream"] = {
+                "unit": "GB/s of packed weight bytes per whole site (weight kernel + finalize), CUDA graph replay",
+                "hbm_peak_gbs": hbm_peak,
+                "sites": {key: {"stream_bytes_per_site": v["stream_bytes_per_site"], "distinct_sites": v["sites"],
+                                "by_tokens": {t: {"site_us": d["site_us"], "gbs": d["site_stream_gbs"],
+                                                  "frac": d["frac_of_hbm"]} for t, d in v["by_tokens"].items()}}
+                          for key, v in sres.items()},
+            }
+        # config 5: the 24-block stack, global batch 8 sharded over the ranks, rank 32, recompute on
+        extras["model_step"] = measure_train_step(dev, world, rank, 24, 8, 32, steps=3, warmup=2)
 
     flops = step_flops(n, k, m, r)
     ms_per_step = total_ms / args.steps
@@ -441,23 +605,10 @@ def run_ours(args):
             peak_src = f"measured ({peak_kind} cuBLAS bf16, MEASURED_PEAKS.json)"
         else:
             peak, peak_src = 1590.0, "fallback (earlier measurement on this pool)"
+        fp8_peak = measure_fp8_peak(dev) if scheme == "fp8" else None
         if fp8c:
-            # No fp8 peak is in MEASURED_PEAKS.json: measure it here the way the bf16 one was measured
-            # (library GEMM, 8192^3, best of 10, CUDA events) and use it as the denominator.
-            a8 = torch.randn(8192, 8192, device=dev).to(torch.float8_e4m3fn)
-            b8 = torch.randn(8192, 8192, device=dev).to(torch.float8_e4m3fn).t()
-            one = torch.ones((), device=dev)
-            best = 1e9
-            for _ in range(13):
-                q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                q0.record()
-                torch._scaled_mm(a8, b8, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
-                q1.record()
-                torch.cuda.synchronize()
-                best = min(best, q0.elapsed_time(q1))
-            peak = 2 * 8192 ** 3 / (best * 1e-3) / 1e12
+            peak = fp8_peak
             peak_src = "measured in this run (burst, torch._scaled_mm e4m3 8192^3, best of 13)"
-            del a8, b8
         gm_ms, gm_n = kinds.get("gemm_main", (0.0, 0))
         achieved = (main_gemm_flops(n, k, m, r) / 2) / (gm_ms / max(gm_n, 1) * 1e-3) / 1e12 if gm_n else None
         roofline = {
@@ -487,12 +638,25 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps},
             "gpu_launches": int(launches),
+            "regions_ms_per_step": [v / args.steps for v in regions_ms],
+            "sustained": {"value": flops * world / (sus_ms / sus_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+                          "seconds": sus_ms * 1e-3, "steps": sus_steps,
+                          "peak": peaks.get("bf16_tflops_sustained"), "sm_mhz_median": sus_mhz,
+                          "frac": (flops / (sus_ms / sus_steps * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"])
+                          if peaks.get("bf16_tflops_sustained") and not fp8c else None},
             "sanity": sanity,
             "native_fp8": native_fp8,
             "model": {"step_flops": flops, "main_gemm_flops": main_gemm_flops(n, k, m, r),
                       "packed_stream_bytes": (k * m + 4 * m) if scheme == "fp8" else (k * m // 2 + 4 * k * m // group)},
             "clocks": clocks,
         }
+        if native_fp8 is not None and fp8_peak:
+            native_fp8["peak"] = fp8_peak
+            native_fp8["peak_source"] = "measured in this run (burst, torch._scaled_mm e4m3 8192^3, best of 13)"
+            native_fp8["frac"] = native_fp8["value"] / world / fp8_peak
+            if native_fp8.get("gemm_tflops"):
+                native_fp8["gemm_frac"] = native_fp8["gemm_tflops"] / fp8_peak
+        line.update(extras)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -510,12 +674,37 @@ def run_stream(args):
     fused_small_fwd_kernel, shared-memory dequant + tcgen05, above)."""
     import torch
 
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    all_results, hbm = measure_stream(dev, max(args.steps, 10))
+    r = 16
+    head = all_results["3072x12288-fp8"]
+    best = head["by_tokens"]["8"]
+    line = {
+        "metric": "packed-weight stream GB/s (cfg2 weight: scaled fp8 3072 -> 12288, forward, 8 tokens)",
+        "value": best["site_stream_gbs"], "unit": "GB/s", "n_gpus": 1, "steps": max(args.steps, 10), "warmup": 3,
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "cfg2-stream", "sites": head["sites"], "d_in": 3072, "d_out": 12288, "rank": r,
+                   "l2": "10 distinct weights = 378 MB > 126 MB L2", "launch": "CUDA graph replay"},
+        # the site is two launches (weight kernel with H = X.A folded in, finalize); per-kernel event times of
+        # launches this short include the launch gap, so the whole-site rate is the one reported against HBM
+        "roofline": {"bound": "hbm", "kernel": "stream_small_fp8_kernel + fused_finalize_kernel (whole site)",
+                     "achieved": best["site_stream_gbs"], "peak": hbm, "unit": "GB/s", "frac": best["site_stream_gbs"] / hbm,
+                     "traffic": None, "algorithmic_bytes_per_launch": head["stream_bytes_per_site"]},
+        "by_site": all_results,
+    }
+    print(json.dumps(line))
+
+
+def measure_stream(dev, reps: int, token_counts=(1, 8, 16, 64)):
+    """The three site shapes of the stream regime at the given token counts; returns
+    ({site: {...}}, hbm peak GB/s).  Every rate carries its fraction of the measured HBM copy rate."""
+    import torch
+
     import loractl_b200 as lb
     from loractl_b200 import _lib as L
     from loractl_b200 import quant as Q
 
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
     lib = L.lib()
     peaks = {}
     if (ROOT / "MEASURED_PEAKS.json").exists():
@@ -536,7 +725,7 @@ def run_stream(args):
         b = torch.randn((r, m), generator=g, device=dev) * 0.01
         stream_bytes = (k * m // 2 + 4 * k * m // 64) if scheme == "int4" else (k * m + 4 * m)
         results = {}
-        for n in ((1, 8, 16, 64) if scheme == "int4" else (1, 8, 16)):
+        for n in (token_counts if scheme == "int4" else tuple(t for t in token_counts if t <= 16)):
             x = torch.randn((n, k), generator=g, device=dev).to(torch.bfloat16)
 
             def chain():
@@ -572,7 +761,6 @@ def run_stream(args):
                 graph.replay()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            reps = max(args.steps, 10)
             e0.record()
             for _ in range(reps):
                 graph.replay()
@@ -583,6 +771,7 @@ def run_stream(args):
             del graph
             results[str(n)] = {
                 "site_us": site_ms * 1e3, "site_stream_gbs": stream_bytes / (site_ms * 1e-3) / 1e9,
+                "frac_of_hbm": stream_bytes / (site_ms * 1e-3) / 1e9 / hbm,
                 "fused_kernel_us": fused_ms * 1e3,
                 "fused_kernel_stream_gbs": stream_bytes / (fused_ms * 1e-3) / 1e9,
                 "by_kernel_us": {kk: v[0] / max(v[1], 1) * 1e3 for kk, v in kinds.items() if v[1]},
@@ -590,22 +779,7 @@ def run_stream(args):
         key = f"{k}x{m}" if scheme == "int4" else f"{k}x{m}-fp8"
         all_results[key] = {"stream_bytes_per_site": stream_bytes, "sites": sites, "scheme": scheme, "by_tokens": results}
         del weights
-    head = all_results["3072x12288-fp8"]
-    best = head["by_tokens"]["8"]
-    line = {
-        "metric": "packed-weight stream GB/s (cfg2 weight: scaled fp8 3072 -> 12288, forward, 8 tokens)",
-        "value": best["site_stream_gbs"], "unit": "GB/s", "n_gpus": 1, "steps": max(args.steps, 10), "warmup": 3,
-        "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "cfg2-stream", "sites": head["sites"], "d_in": 3072, "d_out": 12288, "rank": r,
-                   "l2": "10 distinct weights = 378 MB > 126 MB L2", "launch": "CUDA graph replay"},
-        # the site is two launches (weight kernel with H = X.A folded in, finalize); per-kernel event times of
-        # launches this short include the launch gap, so the whole-site rate is the one reported against HBM
-        "roofline": {"bound": "hbm", "kernel": "stream_small_fp8_kernel + fused_finalize_kernel (whole site)",
-                     "achieved": best["site_stream_gbs"], "peak": hbm, "unit": "GB/s", "frac": best["site_stream_gbs"] / hbm,
-                     "traffic": None, "algorithmic_bytes_per_launch": head["stream_bytes_per_site"]},
-        "by_site": all_results,
-    }
-    print(json.dumps(line))
+    return all_results, hbm
 
 
 def run_load(args):
@@ -705,13 +879,25 @@ def run_load(args):
     print(json.dumps(line))
 
 
-def run_train_step(args):
-    """`--regime step`: LoRA training steps/s of a double-stream MMDiT block stack (the two model
-    workloads: hidden 3072, 24 heads, MLP 12288, every linear int4 block-64 + LoRA, 4096 image + 512
-    text tokens per sample, bf16 activations, block-checkpoint recompute, flow-matching MSE loss),
-    data-parallel over the ranks torchrun started, LoRA gradients all-reduced in one flat bucket.
-    `--blocks`, `--batch` and `--rank` pick the workload: the defaults are the one-block workload (batch 1,
-    rank 16); `--blocks 24 --batch 8 --rank 32` is the full stack."""
+def mmdit_step_flops(cfg, lora_rank: int, n_blocks: int, global_batch: int) -> int:
+    """FLOP model of one training step of the double-stream stack (the counterpart of
+    crates/loractl-core/src/bench.rs:274-311 for this block): linears + LoRA + joint attention,
+    forward + recomputed forward + backward; the frozen weights get no gradient, so a linear's
+    backward is dX only (1x its forward) plus the LoRA terms (2x); attention backward is 2x."""
+    h, tokens = cfg.hidden, cfg.img_tokens + cfg.txt_tokens
+    p_stream = 4 * h * h + 2 * h * cfg.mlp
+    lin_fwd = 2 * tokens * p_stream + 2 * 2 * h * 6 * h  # both streams' projections + the two modulations
+    lora_fwd = 2 * tokens * lora_rank * (2 * h + 4 * h + 2 * h + 2 * (h + cfg.mlp))
+    att_fwd = 4 * tokens * tokens * h
+    flops_block = 2 * (lin_fwd + lora_fwd + att_fwd) + (lin_fwd + 2 * lora_fwd + 2 * att_fwd)
+    return flops_block * n_blocks * global_batch
+
+
+def measure_train_step(dev, world: int, rank: int, n_blocks: int, batch: int, lora_rank: int, steps: int,
+                       warmup: int):
+    """Times `steps` training steps of the double-stream stack on this rank's shard of the global
+    batch (max over ranks, CUDA events, barrier + synchronize on both sides).  Returns the result
+    dict on every rank; the process group, if any, is the caller's."""
     import torch
     import torch.distributed as dist
 
@@ -719,16 +905,8 @@ def run_train_step(args):
     from loractl_b200 import _lib as L
     from loractl_b200.harness import BlockConfig, BlockStack, Trainer
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     cfg = BlockConfig()
-    n_blocks, lora_rank = args.blocks, args.rank
-    global_batch = max(args.batch, world)
+    global_batch = max(batch, world)
     lo, hi = lb.dp.shard_range(global_batch, rank, world)
     b = hi - lo
     stack = BlockStack(n_blocks, cfg, lora_rank, float(lora_rank), dev, seed=5)
@@ -744,7 +922,7 @@ def run_train_step(args):
     def one():
         return trainer.step(x0, txt, cond, t, noise)
 
-    losses = [one() for _ in range(max(args.warmup, 3))]
+    losses = [one() for _ in range(max(warmup, 2))]
     lb.check_device_status(dev)
     if world > 1:
         dist.barrier()
@@ -752,7 +930,7 @@ def run_train_step(args):
     launches0 = L.lib().lq_kernel_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         losses.append(one())
     e1.record()
     if world > 1:
@@ -765,33 +943,146 @@ def run_train_step(args):
         ms = float(tm.item())
     launches = L.lib().lq_kernel_launch_count() - launches0
     lb.check_device_status(dev)
+    tokens = cfg.img_tokens + cfg.txt_tokens
+    step_fl = mmdit_step_flops(cfg, lora_rank, n_blocks, global_batch)
+    n_params = sum(p.numel() for p in stack.lora_parameters())
+    out = {
+        "metric": "MMDiT LoRA train steps/s", "value": steps / (ms * 1e-3), "unit": "steps/s",
+        "n_gpus": world, "steps": steps, "warmup": max(warmup, 2), "ms_per_step": ms / steps,
+        "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "mmdit-double-stream", "blocks": n_blocks, "hidden": h, "heads": cfg.heads,
+                   "mlp": cfg.mlp, "lora_rank": lora_rank, "global_batch": global_batch,
+                   "samples_per_gpu": b, "tokens_per_sample": tokens, "quant": "int4 block 64",
+                   "grad_checkpointing": True, "parallelism": f"dp{world}"},
+        "model": {"step_flops": step_fl, "tflops": step_fl / (ms / steps * 1e-3) / 1e12,
+                  "lora_params": n_params, "grad_bucket_bytes": stack.flat.numel * 4},
+        "tokens_per_s": tokens * global_batch * steps / (ms * 1e-3),
+        "loss_first": losses[0], "loss_last": losses[-1], "gpu_launches": int(launches),
+    }
+    del trainer, stack
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_train_step(args):
+    """`--regime step`: LoRA training steps/s of a double-stream MMDiT block stack (the two model
+    workloads: hidden 3072, 24 heads, MLP 12288, every linear int4 block-64 + LoRA, 4096 image + 512
+    text tokens per sample, bf16 activations, block-checkpoint recompute, flow-matching MSE loss),
+    data-parallel over the ranks torchrun started, LoRA gradients all-reduced in one flat bucket.
+    `--blocks`, `--batch` and `--rank` pick the workload: the defaults are the one-block workload (batch 1,
+    rank 16); `--blocks 24 --batch 8 --rank 32` is the full stack.  `--model gpt2` runs the text
+    workload instead (12 layers, 768 wide, int4 block-64 base, rank 8 on q/k/v/o, batch 8 x 1024)."""
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if args.model == "gpt2":
+        line = measure_gpt2_step(dev, world, rank, args.steps, args.warmup)
+    else:
+        line = measure_train_step(dev, world, rank, args.blocks, args.batch, args.rank, args.steps, args.warmup)
     if rank == 0:
-        tokens = cfg.img_tokens + cfg.txt_tokens
-        p_stream = 4 * h * h + 2 * h * cfg.mlp
-        lin_fwd = 2 * tokens * p_stream + 2 * 2 * h * 6 * h  # both streams' projections + the two modulations
-        lora_fwd = 2 * tokens * lora_rank * (2 * h + 4 * h + 2 * h + 2 * (h + cfg.mlp))
-        att_fwd = 4 * tokens * tokens * h
-        # forward + recomputed forward + backward; the frozen weights get no gradient, so a linear's
-        # backward is dX only (1x its forward) plus the LoRA terms (2x); attention backward is 2x
-        flops_block = 2 * (lin_fwd + lora_fwd + att_fwd) + (lin_fwd + 2 * lora_fwd + 2 * att_fwd)
-        step_fl = flops_block * n_blocks * global_batch
-        n_params = sum(p.numel() for p in stack.lora_parameters())
-        line = {
-            "metric": "MMDiT LoRA train steps/s", "value": args.steps / (ms * 1e-3), "unit": "steps/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "mmdit-double-stream", "blocks": n_blocks, "hidden": h, "heads": cfg.heads,
-                       "mlp": cfg.mlp, "lora_rank": lora_rank, "global_batch": global_batch,
-                       "tokens_per_sample": tokens, "quant": "int4 block 64", "grad_checkpointing": True,
-                       "parallelism": f"dp{world}"},
-            "model": {"step_flops": step_fl, "tflops": step_fl / (ms / args.steps * 1e-3) / 1e12,
-                      "lora_params": n_params, "grad_bucket_bytes": stack.flat.numel * 4},
-            "tokens_per_s": tokens * global_batch * args.steps / (ms * 1e-3),
-            "loss_first": losses[0], "loss_last": losses[-1], "gpu_launches": int(launches),
-        }
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def measure_gpt2_step(dev, world: int, rank: int, steps: int, warmup: int, batch: int = 8, seq: int = 1024):
+    """The text workload: GPT-2-small-shaped decoder (12 layers, 768, 12 heads, MLP 3072, vocabulary
+    50257; crates/loractl-core/src/gpt2.rs:93-103), every per-block projection int4 block 64, LoRA rank 8
+    on q/k/v/o, seeded uniform token ids, next-token cross-entropy, AdamW on the flat adapter bucket;
+    data parallel over the ranks (batch sharded, gradients all-reduced)."""
+    import torch
+    import torch.distributed as dist
+
+    import loractl_b200 as lb
+    from loractl_b200 import _lib as L
+    from loractl_b200 import dp
+    from loractl_b200 import gpt2 as G
+    from loractl_b200.adapters import LoraConfig, TargetSpec, build_adapters
+    from loractl_b200.optim import AdamW, FlatAdapters, nonfinite_flag
+
+    cfg = G.Gpt2Config.gpt2_small()
+    torch.manual_seed(5)
+    model = G.Gpt2(cfg, split_qkv=True).to(dev)
+    with torch.no_grad():
+        gw = torch.Generator(device=dev).manual_seed(5)
+        for _, base in model.base_linears():
+            base.as_plain().weight.copy_(torch.randn(base.as_plain().weight.shape, generator=gw, device=dev) * 0.02)
+            base.as_plain().bias.zero_()
+        model.wte.weight.copy_(torch.randn(model.wte.weight.shape, generator=gw, device=dev) * 0.02)
+        model.wpe.weight.copy_(torch.randn(model.wpe.weight.shape, generator=gw, device=dev) * 0.01)
+    model.into_quantized(4, block=64)
+    model = model.to(torch.bfloat16)
+    lcfg = LoraConfig(rank=8, alpha=8.0, targets=[TargetSpec(r"attn\.(q|k|v|c_proj)$")])
+    torch.manual_seed(5)
+    adapters = build_adapters(model.injectable_sites(), lcfg, dev)
+    with torch.no_grad():
+        g2 = torch.Generator(device=dev).manual_seed(6)
+        for d in adapters.deltas:
+            d.lora_b.copy_(torch.randn(d.lora_b.shape, generator=g2, device=dev) * 0.01)
+    flat = FlatAdapters(adapters, dev)
+    optim = AdamW(flat)
+    global_batch = max(batch, world)
+    lo, hi = dp.shard_range(global_batch, rank, world)
+    gd = torch.Generator(device=dev).manual_seed(100 + rank)
+    ids = torch.randint(0, cfg.vocab_size, (hi - lo, seq), generator=gd, device=dev)
+
+    def one():
+        flat.zero_grad()
+        loss = G.next_token_loss(model(ids, adapters, dtype=torch.bfloat16), ids)
+        loss.backward()
+        flat.gather_autograd_grads()
+        nonfinite_flag(flat.grads, flat.flag)
+        scale = dp.sync_gradients(flat.grads, flat.flag)
+        optim.step(1e-4, grad_scale=scale, skip_flag=flat.flag)
+        return loss
+
+    losses = [float(one()) for _ in range(max(warmup, 3))]
+    lb.check_device_status(dev)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches0 = L.lib().lq_kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    last = None
+    for _ in range(steps):
+        last = one()
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        tm = torch.tensor([ms], device=dev)
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        ms = float(tm.item())
+    launches = L.lib().lq_kernel_launch_count() - launches0
+    lb.check_device_status(dev)
+    e, inner, tok = cfg.n_embd, cfg.n_inner, global_batch * seq
+    lin = 2 * tok * (4 * e * e + 2 * e * inner) * cfg.n_layer          # frozen projections, forward
+    lora = 2 * tok * 8 * (2 * e) * 4 * cfg.n_layer                      # rank-8 down + up on q/k/v/o
+    att = 4 * global_batch * seq * seq * e * cfg.n_layer // 2           # causal: half the score matrix
+    head = 2 * tok * e * cfg.vocab_size
+    step_fl = (lin + lora + att + head) + (lin + 2 * lora + 2 * att + head)  # forward + backward (no weight grads)
+    return {
+        "metric": "text-model LoRA train steps/s", "value": steps / (ms * 1e-3), "unit": "steps/s", "n_gpus": world,
+        "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms / steps, "higher_is_better": True,
+        "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "gpt2-small-shaped decoder", "layers": cfg.n_layer, "hidden": e, "heads": cfg.n_head,
+                   "mlp": inner, "vocab": cfg.vocab_size, "lora_rank": 8, "lora_sites": "q, k, v, o",
+                   "global_batch": global_batch, "seq_len": seq, "quant": "int4 block 64", "parallelism": f"dp{world}"},
+        "model": {"step_flops": step_fl, "tflops": step_fl / (ms / steps * 1e-3) / 1e12,
+                  "lora_params": sum(p.numel() for d in adapters.deltas for p in (d.lora_a, d.lora_b))},
+        "tokens_per_s": tok * steps / (ms * 1e-3), "loss_first": losses[0], "loss_last": float(last),
+        "gpu_launches": int(launches),
+    }
 
 
 def main():
@@ -803,6 +1094,9 @@ def main():
                     help="tensor: the headline fwd+bwd step; stream: packed-weight stream at <= 64 tokens; "
                          "step: LoRA training steps/s of a double-stream MMDiT block stack; "
                          "load: streaming quantize-at-load of one block from a scaled-fp8 checkpoint")
+    ap.add_argument("--model", default="mmdit", choices=["mmdit", "gpt2"], help="--regime step: which caller of the path")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="tensor regime: skip the extra keys (int4_cfg1, stream, model_step) of the default line")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)

@@ -33,7 +33,7 @@ extern "C" {
 #pragma GCC visibility push(default)
 #endif
 
-#define LQ_ABI_VERSION 1
+#define LQ_ABI_VERSION 2
 
 typedef enum lq_status {
     LQ_OK = 0,
@@ -170,10 +170,13 @@ size_t lq_linear_workspace_bytes(const lq_weight_t* w, int64_t n_tokens, int ran
  * (crates/loractl-core/src/quant.rs:172-178) plus bias.  `H_out` (f32 [N, r],
  * may be NULL) receives H = X . A for the backward.  Dropout on the adapter input
  * is not supported (p must be 0; the reference forbids it under recompute,
- * crates/loractl-core/src/diffusion_trainer.rs:342-348). */
+ * crates/loractl-core/src/diffusion_trainer.rs:342-348).  `lora_mirror` (may be NULL): the bf16
+ * operand arrays of A and B kept by the caller, see lq_lora_mirror_update; A and B must still be
+ * passed (paths that compute in f32 read them). */
 int lq_linear_fwd(const lq_weight_t* w, const void* X, int64_t n_tokens, int dtype,
                   const float* A, const float* B, int rank, float scaling,
-                  void* Y, float* H_out, void* workspace, size_t workspace_bytes, void* stream);
+                  void* Y, float* H_out, void* workspace, size_t workspace_bytes, void* stream,
+                  const void* lora_mirror);
 
 /* Backward of lq_linear_fwd — `QuantMatmulT::backward` (crates/loractl-core/src/
  * quant.rs:221-235: dX = dY . dequant(wq), no gradient to the weight) plus the stock
@@ -189,7 +192,19 @@ int lq_linear_fwd(const lq_weight_t* w, const void* X, int64_t n_tokens, int dty
 int lq_linear_bwd(const lq_weight_t* w, const void* dY, const void* X, const float* H,
                   int64_t n_tokens, int dtype, const float* A, const float* B, int rank,
                   float scaling, void* dX, float* dA, float* dB, int accumulate,
-                  void* workspace, size_t workspace_bytes, void* stream);
+                  void* workspace, size_t workspace_bytes, void* stream, const void* lora_mirror);
+
+/* bf16 mirror of one site's LoRA factors.  The reference keeps A and B as f32 `Linear` weights and
+ * lets every forward and backward read them as they are (crates/loractl-core/src/lora.rs:155-166,
+ * 199-203); the tensor-core path wants them as bf16 GEMM operands (A, A^T, B, B^T, zero padded to a
+ * multiple of 64 columns).  Casting them inside each call costs five short launches per site and
+ * pass; the factors only change once per optimizer step, so a trainer may keep this mirror beside
+ * the parameters (lq_lora_mirror_bytes bytes, 256-byte aligned, caller-owned), refresh it with one
+ * launch after each update, and hand it to lq_linear_fwd / lq_linear_bwd.  A stale mirror gives
+ * stale results: refresh it whenever A or B changed. */
+size_t lq_lora_mirror_bytes(int64_t d_in, int64_t d_out, int rank);
+int lq_lora_mirror_update(const float* A, const float* B, int64_t d_in, int64_t d_out, int rank,
+                          void* mirror, void* stream);
 
 /* Builds, once, the transposed copy of a scaled-fp8 weight that the LQ_BF16_W8A8 backward reads
  * ([d_in, d_out] e4m3 bytes, +1 byte per element of resident memory).  Optional: the first

@@ -51,8 +51,10 @@ SIGNATURES = {
     "lq_unpack": (_I, [_P, _P, _P, _P]),
     "lq_dequantize": (_I, [_P, _P, _I, _P]),
     "lq_linear_workspace_bytes": (_SZ, [_P, _I64, _I, _I]),
-    "lq_linear_fwd": (_I, [_P, _P, _I64, _I, _P, _P, _I, _F, _P, _P, _P, _SZ, _P]),
-    "lq_linear_bwd": (_I, [_P, _P, _P, _P, _I64, _I, _P, _P, _I, _F, _P, _P, _P, _I, _P, _SZ, _P]),
+    "lq_linear_fwd": (_I, [_P, _P, _I64, _I, _P, _P, _I, _F, _P, _P, _P, _SZ, _P, _P]),
+    "lq_linear_bwd": (_I, [_P, _P, _P, _P, _I64, _I, _P, _P, _I, _F, _P, _P, _P, _I, _P, _SZ, _P, _P]),
+    "lq_lora_mirror_bytes": (_SZ, [_I64, _I64, _I]),
+    "lq_lora_mirror_update": (_I, [_P, _P, _I64, _I64, _I, _P, _P]),
     "lq_weight_prepare_fp8_backward": (_I, [_P, _P]),
     "lq_grad_nonfinite_flag": (_I, [_P, _I64, _P, _P]),
     "lq_adamw_step": (_I, [_P, _P, _P, _P, _I64, _F, _F, _F, _F, _F, _I64, _F, _P, _P]),

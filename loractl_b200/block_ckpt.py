@@ -11,14 +11,15 @@ forward must equal the captured one) and no dropout on the adapters
 (crates/loractl-core/src/diffusion_trainer.rs:342-348)."""
 from __future__ import annotations
 
-from typing import Callable, Iterable, List, Sequence, Tuple
+from typing import Callable, Iterable, List, Optional, Sequence, Tuple
 
 import torch
 
 
 def checkpointed_step(blocks: Sequence[Callable[[torch.Tensor], torch.Tensor]], x0: torch.Tensor,
                       head_loss: Callable[[torch.Tensor], torch.Tensor], params: Iterable[torch.nn.Parameter],
-                      loss_scale: float = 1.0, keep_existing_grads: bool = False) -> Tuple[float, List[torch.Tensor]]:
+                      loss_scale: float = 1.0, keep_existing_grads: bool = False,
+                      after_block: Optional[Callable[[int], None]] = None) -> Tuple[float, List[torch.Tensor]]:
     """One training step's loss and gradients with block-checkpoint recompute.
 
     blocks     the trunk, each `block(x) -> x` (adapters are closed over, as the reference passes
@@ -26,6 +27,9 @@ def checkpointed_step(blocks: Sequence[Callable[[torch.Tensor], torch.Tensor]], 
     x0         the trunk's input (output of the pre-trunk stage)
     head_loss  final activation -> scalar loss (`LastLayer` + MSE in the reference, :145-156)
     params     the adapter parameters whose gradients are wanted
+    after_block  called with the block index once that block's backward has been enqueued: its adapter
+               gradients are final from then on (a data-parallel trainer starts their all-reduce
+               here, so that it overlaps the replay of the blocks below)
     Returns `(loss, grads)` with `grads[i] = d(loss * loss_scale) / d params[i]`, the same
     quantities `(loss * loss_scale).backward()` of the monolithic step produces.
     """
@@ -53,5 +57,7 @@ def checkpointed_step(blocks: Sequence[Callable[[torch.Tensor], torch.Tensor]], 
         out.backward(gradient=grad_x)  # the reference seeds via (out * g).sum().backward(): same VJP
         grad_x = x2.grad
         block_inputs[i] = None  # release as the sweep passes
+        if after_block is not None:
+            after_block(i)
     grads = [p.grad if p.grad is not None else torch.zeros_like(p) for p in params]
     return loss_value, grads

@@ -399,9 +399,27 @@ size_t lq_linear_workspace_bytes(const lq_weight_t* w, int64_t n_tokens, int ran
     return align256(c.used) + 256;
 }
 
+size_t lq_lora_mirror_bytes(int64_t d_in, int64_t d_out, int rank) {
+    if (d_in <= 0 || d_out <= 0 || rank <= 0 || rank > 256) return 0;
+    return lq_tc_mirror_bytes(d_in, d_out, rank);
+}
+
+int lq_lora_mirror_update(const float* A, const float* B, int64_t d_in, int64_t d_out, int rank, void* mirror,
+                          void* stream) {
+    return guarded([&] {
+        LQ_CHECK_ARG(A && B && mirror, "NULL argument");
+        LQ_CHECK_ARG(d_in > 0 && d_out > 0 && rank >= 1 && rank <= 256, "d_in, d_out must be positive and rank in [1, 256]");
+        LQ_CHECK_ARG(((uintptr_t)mirror & 255) == 0, "mirror must be 256-byte aligned");
+        int dev = 0;
+        LQ_CUDA(cudaGetDevice(&dev));
+        check_sm100(dev);
+        lq_tc_mirror_build(A, B, d_in, d_out, rank, mirror, (cudaStream_t)stream);
+    });
+}
+
 int lq_linear_fwd(const lq_weight_t* w, const void* X, int64_t n_tokens, int dtype, const float* A, const float* B,
                   int rank, float scaling, void* Y, float* H_out, void* workspace, size_t workspace_bytes,
-                  void* stream) {
+                  void* stream, const void* lora_mirror) {
     return guarded([&] {
         check_call(w, n_tokens, dtype, A, B, rank);
         LQ_CHECK_ARG(n_tokens == 0 || (X != nullptr && Y != nullptr), "X / Y pointer is NULL");
@@ -418,7 +436,9 @@ int lq_linear_fwd(const lq_weight_t* w, const void* X, int64_t n_tokens, int dty
             return;
         }
         if (dtype == LQ_BF16 && lq_tc_supported(w, n_tokens, rank)) {
-            lq_tc_fwd(w, X, n_tokens, A, B, rank, scaling, Y, H_out, workspace, workspace_bytes, st);
+            LQ_CHECK_ARG(((uintptr_t)lora_mirror & 255) == 0, "lora_mirror must be 256-byte aligned");
+            lq_tc_fwd(w, X, n_tokens, A, B, rank, scaling, Y, H_out, workspace, workspace_bytes, st,
+                      rank > 0 ? lora_mirror : nullptr);
             return;
         }
         LQ_CHECK_ARG(rank == 0 || workspace != nullptr || H_out != nullptr, "workspace is NULL");
@@ -431,7 +451,7 @@ int lq_linear_fwd(const lq_weight_t* w, const void* X, int64_t n_tokens, int dty
 
 int lq_linear_bwd(const lq_weight_t* w, const void* dY, const void* X, const float* H, int64_t n_tokens, int dtype,
                   const float* A, const float* B, int rank, float scaling, void* dX, float* dA, float* dB,
-                  int accumulate, void* workspace, size_t workspace_bytes, void* stream) {
+                  int accumulate, void* workspace, size_t workspace_bytes, void* stream, const void* lora_mirror) {
     return guarded([&] {
         check_call(w, n_tokens, dtype, A, B, rank);
         if (n_tokens == 0) {
@@ -453,8 +473,9 @@ int lq_linear_bwd(const lq_weight_t* w, const void* dY, const void* X, const flo
             return;
         }
         if (dtype == LQ_BF16 && lq_tc_supported(w, n_tokens, rank)) {
+            LQ_CHECK_ARG(((uintptr_t)lora_mirror & 255) == 0, "lora_mirror must be 256-byte aligned");
             lq_tc_bwd(w, dY, X, H, n_tokens, A, B, rank, scaling, dX, dA, dB, accumulate, workspace, workspace_bytes,
-                      st);
+                      st, rank > 0 ? lora_mirror : nullptr);
             return;
         }
         LQ_CHECK_ARG(rank == 0 || workspace != nullptr, "workspace is NULL");

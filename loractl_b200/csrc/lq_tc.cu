@@ -992,6 +992,58 @@ void cast_pad(const float* in, long long si, long long sj, __nv_bfloat16* out, l
     LQ_CUDA(cudaGetLastError());
 }
 
+// ---- bf16 mirror of one site's LoRA factors ----------------------------------------------------
+// The tensor-core path consumes A and B as four bf16 operand arrays.  Casting them inside every call
+// costs five short launches per forward + backward; the factors change once per optimizer step, so
+// a caller may keep this mirror beside the f32 parameters and refresh it after each update.
+//   At [r, K]    A transposed (B operand of H = X . A, and of the recomputed H)
+//   Bt [M, EXT]  B transposed, zero padded to EXT columns (K extension of the forward GEMM)
+//   Bb [r, M]    B (B operand of dH = s . dY . B^T)
+//   Ap [K, EXT]  A, zero padded (K extension of the dX GEMM)
+struct LoraMirror {
+    __nv_bfloat16 *At, *Bt, *Bb, *Ap;
+    size_t bytes;
+};
+LoraMirror carve_mirror(int64_t K, int64_t M, int r, void* base) {
+    const size_t EXT = (size_t)ext_width(r);
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        size_t o = al256(off);
+        off = o + bytes;
+        return base ? (__nv_bfloat16*)((char*)base + o) : nullptr;
+    };
+    LoraMirror m;
+    m.At = take((size_t)r * K * 2);
+    m.Bt = take((size_t)M * EXT * 2);
+    m.Bb = take((size_t)r * M * 2);
+    m.Ap = take((size_t)K * EXT * 2);
+    m.bytes = al256(off);
+    return m;
+}
+
+__global__ void __launch_bounds__(256) lora_mirror_kernel(const float* __restrict__ A, const float* __restrict__ B,
+                                                          long long K, long long M, int r, int EXT, LoraMirror m) {
+    const long long n0 = (long long)r * K, n1 = M * EXT, n2 = (long long)r * M, n3 = K * EXT;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n0 + n1 + n2 + n3;
+         i += (long long)gridDim.x * blockDim.x) {
+        if (i < n0) {  // At[j, k] = A[k, j]
+            const long long j = i / K, k = i - j * K;
+            m.At[i] = __float2bfloat16(A[k * r + j]);
+        } else if (i < n0 + n1) {  // Bt[mm, j] = B[j, mm]
+            const long long t = i - n0, mm = t / EXT;
+            const int j = (int)(t - mm * EXT);
+            m.Bt[t] = __float2bfloat16(j < r ? B[(long long)j * M + mm] : 0.f);
+        } else if (i < n0 + n1 + n2) {
+            const long long t = i - n0 - n1;
+            m.Bb[t] = __float2bfloat16(B[t]);
+        } else {  // Ap[k, j] = A[k, j]
+            const long long t = i - n0 - n1 - n2, k = t / EXT;
+            const int j = (int)(t - k * EXT);
+            m.Ap[t] = __float2bfloat16(j < r ? A[k * r + j] : 0.f);
+        }
+    }
+}
+
 template <typename OutT>
 void main_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand* a1, const Operand* b1, int64_t K1,
                OutT* Cout, int64_t ldc, int64_t Mg, int64_t Ng, const float* bias, int sm_count, cudaStream_t st) {
@@ -1329,8 +1381,19 @@ int lq_tc_read_status(int device, cudaStream_t st) {
     return v != 0 ? v : v2;
 }
 
+size_t lq_tc_mirror_bytes(int64_t K, int64_t M, int r) { return r > 0 ? carve_mirror(K, M, r, nullptr).bytes : 0; }
+
+void lq_tc_mirror_build(const float* A, const float* B, int64_t K, int64_t M, int r, void* mirror, cudaStream_t st) {
+    LoraMirror m = carve_mirror(K, M, r, mirror);
+    const int EXT = ext_width(r);
+    const long long total = (long long)r * K + M * EXT + (long long)r * M + K * EXT;
+    LqProf prof(LQ_K_PREP, st);
+    lora_mirror_kernel<<<(unsigned)std::min<long long>((total + 255) / 256, 148 * 8), 256, 0, st>>>(A, B, K, M, r, EXT, m);
+    LQ_CUDA(cudaGetLastError());
+}
+
 void lq_tc_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, const float* B, int r, float s, void* Y,
-               float* H_out, void* ws, size_t ws_bytes, cudaStream_t st) {
+               float* H_out, void* ws, size_t ws_bytes, cudaStream_t st, const void* mirror) {
     const int64_t M = w->M, K = w->K;
     DevCtx& ctx = dev_ctx(w->device);
     LQ_CHECK_ARG(ws != nullptr, "workspace is NULL");
@@ -1353,14 +1416,19 @@ void lq_tc_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, con
         return;
     }
     const int EXT = ext_width(r);
-    ForkJoin fj(ctx, st, true);
+    if (mirror) {  // the caller keeps the factors' bf16 operands: nothing to cast
+        const LoraMirror m = carve_mirror(K, M, r, const_cast<void*>(mirror));
+        t.pdown = m.At;
+        t.pext = m.Bt;
+    }
+    ForkJoin fj(ctx, st, !(w4 && mirror));  // nothing is left for a second stream in that case
     fj.fork();
     // side: frozen weight -> bf16 scratch [M, K] (rounds q*scale, resp. LUT*scale, once to bf16),
     //       and B^T [M, EXT] for the K extension
     if (!w4) lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, fj.side());
-    cast_pad(B, 1, M, t.pext, EXT, M, r, EXT, 1.f, fj.side());
+    if (!mirror) cast_pad(B, 1, M, t.pext, EXT, M, r, EXT, 1.f, fj.side());
     // main: H = X . A  (f32 [N, r] for the backward; bf16 s*H, zero padded, as the K extension)
-    cast_pad(A, 1, r, t.pdown, K, r, (int)K, (int)K, 1.f, st);  // A^T [r, K]
+    if (!mirror) cast_pad(A, 1, r, t.pdown, K, r, (int)K, (int)K, 1.f, st);  // A^T [r, K]
     float* Hf = H_out ? H_out : t.Hf;
     skinny_down(X, N, K, K, t.pdown, K, r, 1.f, Hf, t.ext_a, s, t.part, ctx.sm_count, st);
     fj.join(0);
@@ -1375,7 +1443,7 @@ void lq_tc_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, con
 
 void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H, int64_t N, const float* A,
                const float* B, int r, float s, void* dX, float* dA, float* dB, int accumulate, void* ws,
-               size_t ws_bytes, cudaStream_t st) {
+               size_t ws_bytes, cudaStream_t st, const void* mirror) {
     const int64_t M = w->M, K = w->K;
     DevCtx& ctx = dev_ctx(w->device);
     LQ_CHECK_ARG(ws != nullptr, "workspace is NULL");
@@ -1396,19 +1464,25 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
         }
         return;
     }
+    if (mirror) {
+        const LoraMirror m = carve_mirror(K, M, r, const_cast<void*>(mirror));
+        t.pdown = m.Bb;
+        t.pext = m.Ap;
+        t.pdown2 = m.At;
+    }
     ForkJoin fj(ctx, st, true);
     fj.fork();
     // side: what the dX GEMM needs besides dH: W^T [K, M] and A [K, EXT] in bf16
     if (dX) {
         if (!w4) lq_launch_dequant(w, t.wscr, LQ_BF16, M, 1, fj.side());
-        cast_pad(A, r, 1, t.pext, EXT, K, r, EXT, 1.f, fj.side());
+        if (!mirror) cast_pad(A, r, 1, t.pext, EXT, K, r, EXT, 1.f, fj.side());
     }
     fj.record(0);  // the caller's stream waits for this point just before the dX GEMM
     // side, continued (independent of everything on the caller's stream): dB[r, M] = (s*H)^T . dY
     if (dB) {
         const float* Hsrc = H;
         if (!Hsrc) {  // H not kept by the caller: recompute it (own cast buffer: pdown holds B meanwhile)
-            cast_pad(A, 1, r, t.pdown2, K, r, (int)K, (int)K, 1.f, fj.side());
+            if (!mirror) cast_pad(A, 1, r, t.pdown2, K, r, (int)K, (int)K, 1.f, fj.side());
             skinny_down(X, N, K, K, t.pdown2, K, r, 1.f, t.Hf, t.ext_b, s, t.part2, ctx.sm_count, fj.side());
         } else {
             cast_pad(Hsrc, r, 1, t.ext_b, EXT, N, r, EXT, s, fj.side());
@@ -1416,7 +1490,7 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
         skinny_grad(dY, N, M, M, t.ext_b, r, 1.f, dB, 1, accumulate, t.part2, ctx.sm_count, fj.side());
     }
     // main: dH = s * dY . B^T   (f32 [N, r]; bf16 copy as the K extension of the dX GEMM and as dA's operand)
-    cast_pad(B, M, 1, t.pdown, M, r, (int)M, (int)M, 1.f, st);  // B as bf16 [r, M]
+    if (!mirror) cast_pad(B, M, 1, t.pdown, M, r, (int)M, (int)M, 1.f, st);  // B as bf16 [r, M]
     skinny_down(dY, N, M, M, t.pdown, M, r, s, t.dHf, t.ext_a, 1.f, t.part, ctx.sm_count, st);
     if (dX) {  // dX = [dY | dH] . [W^T | A]^T
         fj.wait(0);

@@ -10,11 +10,15 @@
 bool lq_tc_supported(const lq_weight* w, int64_t n_tokens, int rank);
 size_t lq_tc_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank);
 
+// `mirror` (may be NULL): the bf16 operand arrays of this site's LoRA factors, built by
+// lq_tc_mirror_build; with it the calls cast nothing.
 void lq_tc_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, const float* B, int r, float s, void* Y,
-               float* H_out, void* ws, size_t ws_bytes, cudaStream_t st);
+               float* H_out, void* ws, size_t ws_bytes, cudaStream_t st, const void* mirror);
 void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H, int64_t N, const float* A,
                const float* B, int r, float s, void* dX, float* dA, float* dB, int accumulate, void* ws,
-               size_t ws_bytes, cudaStream_t st);
+               size_t ws_bytes, cudaStream_t st, const void* mirror);
+size_t lq_tc_mirror_bytes(int64_t K, int64_t M, int r);
+void lq_tc_mirror_build(const float* A, const float* B, int64_t K, int64_t M, int r, void* mirror, cudaStream_t st);
 
 // Plain bf16 GEMM entry used by tests and probes: C[Mg,Ng] = A . B^T with either operand
 // K-major ([rows, Kg], Kg contiguous) or MN-major ([Kg, rows], rows contiguous).

@@ -36,6 +36,38 @@ def sync_gradients(bucket: torch.Tensor, flag: Optional[torch.Tensor] = None, gr
     return 1.0 / n
 
 
+class BucketReducer:
+    """Per-block gradient buckets reduced while the reverse sweep is still running.
+
+    The flat gradient buffer holds the adapters in registration order, so the gradients of one
+    block are one contiguous slice.  `reduce_slice(lo, hi)` starts a sum-allreduce of that slice as
+    soon as the block's backward has been enqueued (NCCL orders it after the kernels already on the
+    current stream and runs it on its own stream); `finish()` waits for all of them and reduces the
+    non-finite flag.  With one rank everything is a no-op."""
+
+    def __init__(self, bucket: torch.Tensor, group=None):
+        self.bucket, self.group, self.handles = bucket, group, []
+        self.world = world_size(group)
+
+    def reduce_slice(self, lo: int, hi: int) -> None:
+        if self.world > 1 and hi > lo:
+            self.handles.append(dist.all_reduce(self.bucket[lo:hi], op=dist.ReduceOp.SUM, group=self.group,
+                                                async_op=True))
+
+    def finish(self) -> float:
+        """Waits for every slice; returns the scale (`1/world`) that turns the sums into means."""
+        for h in self.handles:
+            h.wait()
+        self.handles = []
+        return 1.0 / self.world
+
+
+def reduce_flag(flag: torch.Tensor, group=None) -> None:
+    """Max-allreduce of the 1-element non-finite flag, so that every rank takes the same decision."""
+    if world_size(group) > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
+
+
 def consensus_step(scaler: DynamicLossScale, flag: torch.Tensor) -> Tuple[bool, Optional[str]]:
     """Reads the (already all-reduced) flag — the one host synchronisation per step, where the
     reference reads its |g| sum (crates/loractl-core/src/diffusion_trainer.rs:1724) — and

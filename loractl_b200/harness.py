@@ -126,6 +126,10 @@ class BlockStack(nn.Module):
         for blk in self.blocks:
             blk.adapters = self.adapters
         self.flat = FlatAdapters(self.adapters, device)
+        # slice of the flat buffers that holds block i's adapters (registration order = block order)
+        per_block = 2 * len(DoubleStreamBlock.STREAMS) * len(DoubleStreamBlock.LINEARS)
+        offs = self.flat.offsets + [self.flat.numel]
+        self.block_slices = [(offs[i * per_block], offs[(i + 1) * per_block]) for i in range(n_blocks)]
 
     def lora_parameters(self):
         return [p for d in self.adapters.deltas for p in (d.lora_a, d.lora_b)]
@@ -166,16 +170,28 @@ class Trainer:
         head = lambda s: ((s[:, :li].float() - target) ** 2).mean()
         flat.zero_grad()
         params = stack.lora_parameters()
+        reducer = dp.BucketReducer(flat.grads, self.group)
         if self.grad_checkpointing:
+            # a block's gradients are final once its replayed backward is enqueued: their all-reduce
+            # starts there and overlaps the replay of the blocks below it
+            def after_block(i: int) -> None:
+                if reducer.world > 1:
+                    flat.gather_autograd_grads(stack.block_slices[i])
+                    reducer.reduce_slice(*stack.block_slices[i])
+
             loss, _ = checkpointed_step(list(stack.blocks), state, head, params, self.scaler.loss_scale,
-                                        keep_existing_grads=True)
+                                        keep_existing_grads=True, after_block=after_block)
+            flat.gather_autograd_grads()
         else:
             loss_t = head(stack(state))
             (loss_t * self.scaler.loss_scale).backward()
             loss = float(loss_t.detach())
-        flat.gather_autograd_grads()
+            flat.gather_autograd_grads()
+            reducer.reduce_slice(0, flat.numel)
+        # non-finite values survive the sum, so the flag is taken on the reduced gradients
+        scale = reducer.finish()
         nonfinite_flag(flat.grads, flat.flag)
-        scale = dp.sync_gradients(flat.grads, flat.flag, self.group)
+        dp.reduce_flag(flat.flag, self.group)
         # the optimizer reads the flag on the device and skips itself; the host reads it only to
         # advance the loss-scale state (where the reference reads its |g| sum back)
         self.optim.step(self.lr, grad_scale=scale / self.scaler.loss_scale, skip_flag=flat.flag)

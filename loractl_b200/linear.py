@@ -91,9 +91,9 @@ class _LoraLinearFn(torch.autograd.Function):
     state (quant.rs:217-219), never a graph parent."""
 
     @staticmethod
-    def forward(ctx, x2, a, b, wq, scaling):
-        y, h = Q.linear_fwd_raw(wq, x2, a, b, scaling)
-        ctx.wq, ctx.scaling = wq, scaling
+    def forward(ctx, x2, a, b, wq, scaling, mirror):
+        y, h = Q.linear_fwd_raw(wq, x2, a, b, scaling, mirror=mirror)
+        ctx.wq, ctx.scaling, ctx.mirror = wq, scaling, mirror
         ctx.save_for_backward(x2, h, a, b)
         return y
 
@@ -102,8 +102,8 @@ class _LoraLinearFn(torch.autograd.Function):
         x2, h, a, b = ctx.saved_tensors
         need_dx, need_da, need_db = ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.needs_input_grad[2]
         dx, da, db = Q.linear_bwd_raw(ctx.wq, dy.contiguous(), x2, h, a, b, ctx.scaling,
-                                      need_dx=need_dx, need_da=need_da, need_db=need_db)
-        return dx, da, db, None, None
+                                      need_dx=need_dx, need_da=need_da, need_db=need_db, mirror=ctx.mirror)
+        return dx, da, db, None, None, None
 
 
 def _fused(wq: Q.QuantWeight, x: torch.Tensor, delta: Optional[LoraDelta]) -> torch.Tensor:
@@ -120,7 +120,9 @@ def _fused(wq: Q.QuantWeight, x: torch.Tensor, delta: Optional[LoraDelta]) -> to
             raise RuntimeError(
                 "lora.dropout > 0 is not supported on a quantized site of the b200 backend "
                 "(the fused kernel has no dropout; the reference also forbids it under recompute)")
-        y = _LoraLinearFn.apply(x2, delta.lora_a, delta.lora_b, wq, delta.scaling)
+        # bf16 activations take the tensor-core path, which wants the factors as bf16 operands
+        mirror = delta.operand_mirror() if x2.dtype == torch.bfloat16 else None
+        y = _LoraLinearFn.apply(x2, delta.lora_a, delta.lora_b, wq, delta.scaling, mirror)
     return y.reshape(*lead, wq.d_out)
 
 

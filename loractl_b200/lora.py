@@ -36,6 +36,25 @@ class LoraDelta(nn.Module):
         self.scaling = float(alpha) / rank
         self.dropout = float(dropout_prob)
         self.rank = rank
+        # bf16 operand mirror of (lora_a, lora_b) for the tensor-core path, rebuilt when the factors
+        # change; `param_epoch` is bumped by writers that bypass torch (the fused AdamW kernel)
+        self._mirror: Optional[torch.Tensor] = None
+        self._mirror_key = None
+        self.param_epoch = [0]
+
+    def operand_mirror(self) -> Optional[torch.Tensor]:
+        """The factors as bf16 GEMM operands (`lq_lora_mirror_update`), refreshed with one launch
+        whenever `lora_a` / `lora_b` changed since it was built; None off the GPU."""
+        a, b = self.lora_a, self.lora_b
+        if not a.is_cuda:
+            return None
+        key = (a._version, b._version, a.data_ptr(), b.data_ptr(), self.param_epoch[0])
+        if self._mirror is None or self._mirror_key != key:
+            from . import quant as Q
+
+            self._mirror = Q.lora_mirror(a.detach(), b.detach(), self._mirror)
+            self._mirror_key = key
+        return self._mirror
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """The stand-alone delta (lora.rs:199-203), in plain tensor ops.  The fused kernel path

@@ -76,6 +76,9 @@ class FlatAdapters:
             p.data = seg
             p.grad = self.grads[o:o + p.numel()].view(p.shape)
         self._params = params
+        self.param_epoch = [0]  # shared with every delta: bumped when a kernel rewrites `params`
+        for d in adapters.deltas:
+            d.param_epoch = self.param_epoch
 
     def grad_views(self, index: int):
         """(dA view, dB view) of delta `index` — pass them to `lq_linear_bwd` as outputs."""
@@ -88,9 +91,12 @@ class FlatAdapters:
             if p.grad is None or p.grad.data_ptr() != self.grads.data_ptr() + 4 * o:
                 p.grad = self.grads[o:o + p.numel()].view(p.shape)
 
-    def gather_autograd_grads(self) -> None:
-        """If autograd accumulated into separate `.grad` tensors, fold them back into the bucket."""
+    def gather_autograd_grads(self, only: Optional[tuple] = None) -> None:
+        """If autograd accumulated into separate `.grad` tensors, fold them back into the bucket
+        (`only` = (lo, hi): just the parameters whose segment starts inside that slice)."""
         for p, o in zip(self._params, self.offsets):
+            if only is not None and not (only[0] <= o < only[1]):
+                continue
             if p.grad is not None and p.grad.data_ptr() != self.grads.data_ptr() + 4 * o:
                 self.grads[o:o + p.numel()].view(p.shape).copy_(p.grad)
                 p.grad = self.grads[o:o + p.numel()].view(p.shape)
@@ -131,3 +137,4 @@ class AdamW:
                 f.params.data_ptr(), f.grads.data_ptr(), f.exp_avg.data_ptr(), f.exp_avg_sq.data_ptr(), f.numel,
                 float(lr), self.beta1, self.beta2, self.eps, float(self.weight_decay), max(self.steps, 1),
                 float(grad_scale), skip_flag.data_ptr() if skip_flag is not None else None, _stream(f.params)))
+        f.param_epoch[0] += 1  # the kernel wrote through raw pointers: bf16 operand mirrors are stale

@@ -236,8 +236,27 @@ def _compute_code(t: torch.Tensor, fp8_compute: bool) -> int:
     return dt
 
 
+def lora_mirror(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 operand mirror of one site's factors (`lq_lora_mirror_update`): `a` is `[d_in, r]`, `b` is
+    `[r, d_out]`, both f32 on the device.  Returns the (256-byte aligned) byte buffer to pass as
+    `mirror=` to `linear_fwd_raw` / `linear_bwd_raw`; pass `out` to refresh an existing one in place."""
+    _require_cuda(a, "lora_a")
+    d_in, r = a.shape
+    d_out = b.shape[1]
+    need = int(L.lib().lq_lora_mirror_bytes(d_in, d_out, r))
+    if out is None:
+        raw = torch.empty(need + 256, dtype=torch.uint8, device=a.device)
+        off = (-raw.data_ptr()) % 256
+        out = raw[off:off + need]
+    with torch.cuda.device(a.device):
+        L.check(L.lib().lq_lora_mirror_update(a.data_ptr(), b.data_ptr(), d_in, d_out, r, out.data_ptr(),
+                                              _stream_ptr(a.device)))
+    return out
+
+
 def linear_fwd_raw(wq: QuantWeight, x2: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor],
-                   scaling: float, want_h: bool = True, fp8_compute: bool = False):
+                   scaling: float, want_h: bool = True, fp8_compute: bool = False,
+                   mirror: Optional[torch.Tensor] = None):
     """Direct call of `lq_linear_fwd` on a flattened `[N, K]` activation.  Returns (y, h).
     `fp8_compute` selects LQ_BF16_W8A8 (tcgen05 e4m3 x e4m3; scaled-fp8 weights only)."""
     _require_cuda(x2, "x")
@@ -252,7 +271,8 @@ def linear_fwd_raw(wq: QuantWeight, x2: torch.Tensor, a: Optional[torch.Tensor],
         L.check(L.lib().lq_linear_fwd(
             wq.handle, x2.data_ptr(), n, dt,
             a.data_ptr() if rank else None, b.data_ptr() if rank else None, rank, float(scaling),
-            y.data_ptr(), h.data_ptr() if h is not None else None, wp, wn, _stream_ptr(x2.device)))
+            y.data_ptr(), h.data_ptr() if h is not None else None, wp, wn, _stream_ptr(x2.device),
+            mirror.data_ptr() if (mirror is not None and rank) else None))
     return y, h
 
 
@@ -260,7 +280,7 @@ def linear_bwd_raw(wq: QuantWeight, dy2: torch.Tensor, x2: Optional[torch.Tensor
                    a: Optional[torch.Tensor], b: Optional[torch.Tensor], scaling: float,
                    need_dx: bool = True, need_da: bool = True, need_db: bool = True,
                    da_out: Optional[torch.Tensor] = None, db_out: Optional[torch.Tensor] = None,
-                   accumulate: bool = False, fp8_compute: bool = False):
+                   accumulate: bool = False, fp8_compute: bool = False, mirror: Optional[torch.Tensor] = None):
     """Direct call of `lq_linear_bwd`.  Returns (dx, da, db).  `da_out`/`db_out` let the caller
     point the gradients into a flat bucket (with `accumulate` to add instead of overwrite)."""
     n = dy2.shape[0]
@@ -282,7 +302,8 @@ def linear_bwd_raw(wq: QuantWeight, dy2: torch.Tensor, x2: Optional[torch.Tensor
             h.data_ptr() if h is not None else None, n, dt,
             a.data_ptr() if rank else None, b.data_ptr() if rank else None, rank, float(scaling),
             dx.data_ptr() if dx is not None else None, da.data_ptr() if da is not None else None,
-            db.data_ptr() if db is not None else None, 1 if accumulate else 0, wp, wn, _stream_ptr(dev)))
+            db.data_ptr() if db is not None else None, 1 if accumulate else 0, wp, wn, _stream_ptr(dev),
+            mirror.data_ptr() if (mirror is not None and rank) else None))
     return dx, da, db
 
 

@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(lib, n), f"{n} is declared in include/loractl_b200.h but not exported"
     assert sorted(L.SIGNATURES) == names, "ctypes SIGNATURES and the header disagree"
-    assert lib.lq_abi_version() == 1
+    assert lib.lq_abi_version() == 2
 
 
 def test_dequant_chunk_rows_through_the_c_abi():
@@ -43,7 +43,7 @@ def test_dequant_chunk_rows_through_the_c_abi():
 def test_no_cpu_path_and_null_handle_errors():
     with pytest.raises(RuntimeError, match="no CPU path"):
         lb.quantize_linear_weight(torch.zeros(4, 64), 4)
-    rc = L.lib().lq_linear_fwd(None, None, 4, 0, None, None, 0, 1.0, None, None, None, 0, None)
+    rc = L.lib().lq_linear_fwd(None, None, 4, 0, None, None, 0, 1.0, None, None, None, 0, None, None)
     assert rc == L.LQ_ERR_INVALID and b"quantized weight" in L.lib().lq_last_error()
     assert L.lib().lq_linear_workspace_bytes(None, 4, 0, 0) == 0
 

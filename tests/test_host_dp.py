@@ -101,3 +101,42 @@ def test_shard_range_partitions_the_batch(batch, world):
     assert all(spans[i][1] == spans[i + 1][0] for i in range(world - 1))
     sizes = [b - a for a, b in spans]
     assert max(sizes) - min(sizes) <= 1 and sizes == sorted(sizes, reverse=True)
+
+
+def _bucket_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # three "blocks" of a flat bucket, reduced from the last block to the first as a reverse
+        # sweep would, each slice as soon as it is final
+        bucket = torch.arange(12, dtype=torch.float32) * (rank + 1)
+        red = dp.BucketReducer(bucket)
+        for lo, hi in ((8, 12), (3, 8), (0, 3)):
+            red.reduce_slice(lo, hi)
+        scale = red.finish()
+        flag = torch.tensor([1 if rank == 1 else 0], dtype=torch.int32)
+        dp.reduce_flag(flag)
+        out.put((rank, bucket.tolist(), scale, int(flag.item())))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_per_block_buckets_equal_one_flat_allreduce():
+    world = 2
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_bucket_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(out.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    want = [float(i) * 3 for i in range(12)]  # rank 0 contributes i, rank 1 contributes 2 i
+    for rank, bucket, scale, flag in res:
+        assert bucket == want and scale == 0.5 and flag == 1
+    # one rank: nothing to reduce, scale 1
+    red = dp.BucketReducer(torch.ones(4))
+    red.reduce_slice(0, 4)
+    assert red.finish() == 1.0
