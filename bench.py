@@ -894,7 +894,7 @@ def mmdit_step_flops(cfg, lora_rank: int, n_blocks: int, global_batch: int) -> i
 
 
 def measure_train_step(dev, world: int, rank: int, n_blocks: int, batch: int, lora_rank: int, steps: int,
-                       warmup: int):
+                       warmup: int, weight_copies: bool = False):
     """Times `steps` training steps of the double-stream stack on this rank's shard of the global
     batch (max over ranks, CUDA events, barrier + synchronize on both sides).  Returns the result
     dict on every rank; the process group, if any, is the caller's."""
@@ -909,7 +909,7 @@ def measure_train_step(dev, world: int, rank: int, n_blocks: int, batch: int, lo
     global_batch = max(batch, world)
     lo, hi = lb.dp.shard_range(global_batch, rank, world)
     b = hi - lo
-    stack = BlockStack(n_blocks, cfg, lora_rank, float(lora_rank), dev, seed=5)
+    stack = BlockStack(n_blocks, cfg, lora_rank, float(lora_rank), dev, seed=5, weight_copies=weight_copies)
     trainer = Trainer(stack, lr=1e-4)
     g = torch.Generator(device=dev).manual_seed(100 + rank)  # per-rank data, identical weights
     h = cfg.hidden
@@ -953,7 +953,9 @@ def measure_train_step(dev, world: int, rank: int, n_blocks: int, batch: int, lo
         "config": {"workload": "mmdit-double-stream", "blocks": n_blocks, "hidden": h, "heads": cfg.heads,
                    "mlp": cfg.mlp, "lora_rank": lora_rank, "global_batch": global_batch,
                    "samples_per_gpu": b, "tokens_per_sample": tokens, "quant": "int4 block 64",
-                   "grad_checkpointing": True, "parallelism": f"dp{world}"},
+                   "grad_checkpointing": True, "parallelism": f"dp{world}",
+                   "weight_copies": "resident bf16 copy of every frozen weight (no dequantisation pass)"
+                   if weight_copies else "none (every call dequantises into the workspace)"},
         "model": {"step_flops": step_fl, "tflops": step_fl / (ms / steps * 1e-3) / 1e12,
                   "lora_params": n_params, "grad_bucket_bytes": stack.flat.numel * 4},
         "tokens_per_s": tokens * global_batch * steps / (ms * 1e-3),
@@ -985,7 +987,8 @@ def run_train_step(args):
     if args.model == "gpt2":
         line = measure_gpt2_step(dev, world, rank, args.steps, args.warmup)
     else:
-        line = measure_train_step(dev, world, rank, args.blocks, args.batch, args.rank, args.steps, args.warmup)
+        line = measure_train_step(dev, world, rank, args.blocks, args.batch, args.rank, args.steps, args.warmup,
+                                  weight_copies=args.weight_copies)
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -1095,6 +1098,8 @@ def main():
                          "step: LoRA training steps/s of a double-stream MMDiT block stack; "
                          "load: streaming quantize-at-load of one block from a scaled-fp8 checkpoint")
     ap.add_argument("--model", default="mmdit", choices=["mmdit", "gpt2"], help="--regime step: which caller of the path")
+    ap.add_argument("--weight-copies", action="store_true",
+                    help="--regime step: keep a resident bf16 copy of every frozen weight (no dequantisation pass)")
     ap.add_argument("--no-extras", action="store_true",
                     help="tensor regime: skip the extra keys (int4_cfg1, stream, model_step) of the default line")
     ap.add_argument("--gpus", type=int, default=1)

@@ -152,6 +152,21 @@ int lq_unpack(const lq_weight_t* w, int8_t* codes, float* scales, void* stream);
  * crates/loractl-core/src/fp8.rs:305-317) computed in f32, stored as out_dtype. */
 int lq_dequantize(const lq_weight_t* w, void* out, int out_dtype, void* stream);
 
+/* A resident bf16 copy of the dequantised weight, [d_out, d_in] row-major, in a caller-owned buffer
+ * of lq_weight_bf16_copy_bytes() bytes (16-byte aligned, d_in % 8 == 0).  The reference dequantises
+ * the whole weight to f32 inside every forward and every backward (crates/loractl-core/src/
+ * quant.rs:232,250); the LQ_BF16 tensor-regime calls normally do the same into the caller's
+ * workspace, in bf16.  A GPU with 180 GB can afford to keep that copy: while one is attached the
+ * calls read it directly — the forward as a K-major operand, the backward (reduction over d_out) as
+ * an MN-major operand of the same buffer — and run no dequantisation pass at all.  The values are
+ * the same bf16(q * scale), so results do not change.  `lq_weight_attach_bf16_copy` fills the
+ * buffer (one pass, stream-ordered) and attaches it; buffer = NULL detaches.  A trainer may attach
+ * for the whole run (2 bytes per element resident) or around one block's replay under block
+ * checkpointing (one pass instead of two per site).  Load-time call: do not attach or detach while
+ * another thread runs calls on the same handle. */
+size_t lq_weight_bf16_copy_bytes(const lq_weight_t* w);
+int lq_weight_attach_bf16_copy(lq_weight_t* w, void* buffer, void* stream);
+
 /* ---- the hot path ----------------------------------------------------------- */
 
 /* Scratch the two calls below need for this (weight, N, rank, dtype); the caller

@@ -53,6 +53,8 @@ SIGNATURES = {
     "lq_linear_workspace_bytes": (_SZ, [_P, _I64, _I, _I]),
     "lq_linear_fwd": (_I, [_P, _P, _I64, _I, _P, _P, _I, _F, _P, _P, _P, _SZ, _P, _P]),
     "lq_linear_bwd": (_I, [_P, _P, _P, _P, _I64, _I, _P, _P, _I, _F, _P, _P, _P, _I, _P, _SZ, _P, _P]),
+    "lq_weight_bf16_copy_bytes": (_SZ, [_P]),
+    "lq_weight_attach_bf16_copy": (_I, [_P, _P, _P]),
     "lq_lora_mirror_bytes": (_SZ, [_I64, _I64, _I]),
     "lq_lora_mirror_update": (_I, [_P, _P, _I64, _I64, _I, _P, _P]),
     "lq_weight_prepare_fp8_backward": (_I, [_P, _P]),

@@ -399,6 +399,23 @@ size_t lq_linear_workspace_bytes(const lq_weight_t* w, int64_t n_tokens, int ran
     return align256(c.used) + 256;
 }
 
+size_t lq_weight_bf16_copy_bytes(const lq_weight_t* w) { return w ? (size_t)w->M * (size_t)w->K * 2 : 0; }
+
+int lq_weight_attach_bf16_copy(lq_weight_t* w, void* buffer, void* stream) {
+    return guarded([&] {
+        LQ_CHECK_ARG(w != nullptr, "weight handle is NULL");
+        if (!buffer) {  // detach: per-call dequantisation again
+            w->bf16_copy = nullptr;
+            return;
+        }
+        LQ_CHECK_ARG(((uintptr_t)buffer & 15) == 0, "bf16 copy must be 16-byte aligned");
+        LQ_CHECK_ARG(w->K % 8 == 0, "bf16 copy needs d_in % 8 == 0 (16-byte rows)");
+        DeviceGuard dg(w->device);
+        lq_launch_dequant(w, buffer, LQ_BF16, w->K, 0, (cudaStream_t)stream);
+        w->bf16_copy = buffer;
+    });
+}
+
 size_t lq_lora_mirror_bytes(int64_t d_in, int64_t d_out, int rank) {
     if (d_in <= 0 || d_out <= 0 || rank <= 0 || rank > 256) return 0;
     return lq_tc_mirror_bytes(d_in, d_out, rank);

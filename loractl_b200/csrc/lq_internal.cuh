@@ -38,6 +38,7 @@ struct lq_weight {
     float* bias = nullptr;
     size_t packed_bytes = 0, scale_bytes = 0;
     void* packed_t = nullptr;  // fp8 only: the bytes transposed to [d_in, d_out], built on first use
+    const void* bf16_copy = nullptr;  // optional caller-owned bf16 [d_out, d_in] copy of the dequantised weight
 };
 
 // Device-side view passed to kernels by value.

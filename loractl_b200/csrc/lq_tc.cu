@@ -346,7 +346,11 @@ struct Cfg2 {
     static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + STAGE_OUT + 1024 + 256;
 };
 
-template <int BLOCK_N, bool F8>
+// B_MN: the B operand of the first tensor-map pair is MN-major ([Kg, Ng] in memory, Ng contiguous) —
+// the frozen weight's bf16 copy [d_out, d_in] read as the B operand of dX = dY . W, whose reduction
+// runs over d_out: each CTA loads its 128 columns as two 64-column boxes of 64 reduction rows.  The
+// K-extension pair stays K-major.  bf16 only, BLOCK_N = 256 only.
+template <int BLOCK_N, bool F8, bool B_MN = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
                   const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
@@ -354,6 +358,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
     using C = Cfg2<BLOCK_N>;
     constexpr int STAGES = C::STAGES;
     constexpr int BK0 = F8 ? 128 : BK;
+    static_assert(!B_MN || (!F8 && BLOCK_N == 256), "MN-major B: bf16, 256-column tiles");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_a = smem;
@@ -418,8 +423,15 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
                     const CUtensorMap* mb = ext ? &tmB1 : &tmB0;
                     const int kc = ext ? (kb - p.kb0) * BK : kb * BK0;
                     tma_load_2d_pair(smem_u32(smem_a + (size_t)s * C::A_BYTES), ma, bar, kc, m_tile * 256 + (int)rank * BM);
-                    tma_load_2d_pair(smem_u32(smem_b + (size_t)s * C::B_BYTES), mb, bar, kc,
-                                     n_tile * BLOCK_N + (int)rank * (BLOCK_N / 2));
+                    if (B_MN && !ext) {
+#pragma unroll
+                        for (int c = 0; c < BLOCK_N / 128; ++c)  // 64-column chunks of this CTA's half, 64 reduction rows each
+                            tma_load_2d_pair(smem_u32(smem_b + (size_t)s * C::B_BYTES) + c * 8192, mb, bar,
+                                             n_tile * BLOCK_N + (int)rank * (BLOCK_N / 2) + c * 64, kc);
+                    } else {
+                        tma_load_2d_pair(smem_u32(smem_b + (size_t)s * C::B_BYTES), mb, bar, kc,
+                                         n_tile * BLOCK_N + (int)rank * (BLOCK_N / 2));
+                    }
                     if (++s == STAGES) { s = 0; phase ^= 1u; }
                 }
             }
@@ -430,10 +442,12 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
         if (lane == 0 && leader) {
             // ---------------- MMA issuer (leader CTA only) ----------------
             constexpr uint32_t idesc = make_idesc(1, 1, false, false, 256, BLOCK_N);
+            constexpr uint32_t idesc_mn = make_idesc(1, 1, false, true, 256, BLOCK_N);
             constexpr uint32_t idesc8 = make_idesc(0, 0, false, false, 256, BLOCK_N);
             const uint32_t d_hi = desc_hi(1024);
             const uint32_t a_lo0 = desc_lo(smem_u32(smem_a), 16);
             const uint32_t b_lo0 = desc_lo(smem_u32(smem_b), 16);
+            const uint32_t b_lo0_mn = desc_lo(smem_u32(smem_b), 8192);
             int s = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
@@ -451,6 +465,12 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
                         for (int k = 0; k < 4; ++k)
                             mma2_f8(tmem_d, desc_join(a_lo + k * 2u, d_hi), desc_join(b_lo + k * 2u, d_hi), idesc8,
                                     (kb > 0 || k > 0) ? 1u : 0u);
+                    } else if (B_MN && kb < p.kb0) {
+                        const uint32_t bm_lo = b_lo0_mn + (uint32_t)s * (C::B_BYTES >> 4);
+#pragma unroll
+                        for (int k = 0; k < BK / 16; ++k)  // 16 reduction rows of 128 bytes per step
+                            mma2_f16(tmem_d, desc_join(a_lo + k * 2u, d_hi), desc_join(bm_lo + k * 128u, d_hi), idesc_mn,
+                                     (kb > 0 || k > 0) ? 1u : 0u);
                     } else {
 #pragma unroll
                         for (int k = 0; k < BK / 16; ++k)
@@ -814,7 +834,7 @@ bool pair_enabled() {
 }
 
 // The frozen GEMM on CTA pairs: 256 x BLOCK_N tiles, K-major operands, bf16 output through TMA stores.
-template <int BLOCK_N, bool F8>
+template <int BLOCK_N, bool F8, bool B_MN = false>
 void launch_gemm_pair(const Operand& a0, const Operand& b0, int64_t K0, const Operand* a1, const Operand* b1, int64_t K1,
                       __nv_bfloat16* Cout, int64_t ldc, int64_t Mg, int64_t Ng, const float* bias, cudaStream_t st,
                       EpiScales sc = EpiScales()) {
@@ -823,7 +843,8 @@ void launch_gemm_pair(const Operand& a0, const Operand& b0, int64_t K0, const Op
     LQ_CUDA(cudaGetDevice(&dev));
     DevCtx& ctx = dev_ctx(dev);
     CUtensorMap tA0 = make_map(a0.ptr, K0, Mg, a0.ld, BM, F8);
-    CUtensorMap tB0 = make_map(b0.ptr, K0, Ng, b0.ld, BLOCK_N / 2, F8);
+    // MN-major B: [K0 rows of the reduction, Ng columns] in memory, boxes of 64 columns x 64 rows
+    CUtensorMap tB0 = B_MN ? make_map(b0.ptr, Ng, K0, b0.ld, 64) : make_map(b0.ptr, K0, Ng, b0.ld, BLOCK_N / 2, F8);
     CUtensorMap tA1 = a1 ? make_map(a1->ptr, K1, Mg, a1->ld, BM) : tA0;
     CUtensorMap tB1 = b1 ? make_map(b1->ptr, K1, Ng, b1->ld, BLOCK_N / 2) : tB0;
     constexpr int BK0 = F8 ? 128 : BK;
@@ -847,7 +868,7 @@ void launch_gemm_pair(const Operand& a0, const Operand& b0, int64_t K0, const Op
     CUtensorMap tC = make_store_map(Cout, Ng, Mg, ldc);
     const long long items = (long long)p.m_tiles * p.n_tiles;
     p.group_m = lq_tc_pair_group_m(ctx.sm_count, BLOCK_N, Ng, K0, F8 ? 1 : 2, p.n_tiles);
-    auto kern = umma_gemm2_kernel<BLOCK_N, F8>;
+    auto kern = umma_gemm2_kernel<BLOCK_N, F8, B_MN>;
     LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
     // persistent grid = the number of CTA pairs that can be resident at once (asked once per device)
     static std::mutex mu;
@@ -1405,13 +1426,15 @@ void lq_tc_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, con
     Operand a0{X, false, K}, b0{t.wscr, false, K};
     // int4 weights at tile-filling sizes: the weight is converted inside the GEMM's mainloop and no
     // bf16 copy of it is written; otherwise it is dequantised once per call into the scratch
-    const bool w4 = lq_w4_supported(w, N, 0);
+    const bool w4 = !w->bf16_copy && lq_w4_supported(w, N, 0);
+    const bool cached = w->bf16_copy != nullptr;  // a resident bf16 copy stands in for the per-call scratch
+    if (cached) b0.ptr = w->bf16_copy;
     if (r == 0) {
         if (w4) {
             lq_w4_gemm(w, 0, X, K, nullptr, 0, nullptr, 0, 0, Y, M, N, w->bias, st);
             return;
         }
-        lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, st);
+        if (!cached) lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, st);
         main_gemm<__nv_bfloat16>(a0, b0, K, nullptr, nullptr, 0, (__nv_bfloat16*)Y, M, N, M, w->bias, ctx.sm_count, st);
         return;
     }
@@ -1421,11 +1444,11 @@ void lq_tc_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, con
         t.pdown = m.At;
         t.pext = m.Bt;
     }
-    ForkJoin fj(ctx, st, !(w4 && mirror));  // nothing is left for a second stream in that case
+    ForkJoin fj(ctx, st, !((w4 || cached) && mirror));  // nothing is left for a second stream in that case
     fj.fork();
     // side: frozen weight -> bf16 scratch [M, K] (rounds q*scale, resp. LUT*scale, once to bf16),
     //       and B^T [M, EXT] for the K extension
-    if (!w4) lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, fj.side());
+    if (!w4 && !cached) lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, fj.side());
     if (!mirror) cast_pad(B, 1, M, t.pext, EXT, M, r, EXT, 1.f, fj.side());
     // main: H = X . A  (f32 [N, r] for the backward; bf16 s*H, zero padded, as the K extension)
     if (!mirror) cast_pad(A, 1, r, t.pdown, K, r, (int)K, (int)K, 1.f, st);  // A^T [r, K]
@@ -1454,10 +1477,16 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
                                             std::to_string(ws_bytes));
     const int EXT = ext_width(r > 0 ? r : 1);
     Operand a0{dY, false, M}, b0{t.wscr, false, M};
-    const bool w4 = dX && lq_w4_supported(w, N, 1);
+    const bool w4 = dX && !w->bf16_copy && lq_w4_supported(w, N, 1);
+    // a resident bf16 copy [M, K] is read as an MN-major B operand (reduction over its rows) by the
+    // CTA-pair kernel: no transposed scratch is written
+    const bool cached = dX && w->bf16_copy && pair_enabled() && N >= 256 && K > 192 && ctx.sm_count >= 2;
+    Operand bmn{w->bf16_copy, true, K};
     if (r == 0) {
         if (dX && w4) {
             lq_w4_gemm(w, 1, dY, M, nullptr, 0, nullptr, 0, 0, dX, K, N, nullptr, st);
+        } else if (dX && cached) {
+            launch_gemm_pair<256, false, true>(a0, bmn, M, nullptr, nullptr, 0, (__nv_bfloat16*)dX, K, N, K, nullptr, st);
         } else if (dX) {
             lq_launch_dequant(w, t.wscr, LQ_BF16, M, 1, st);  // W^T [K, M]
             main_gemm<__nv_bfloat16>(a0, b0, M, nullptr, nullptr, 0, (__nv_bfloat16*)dX, K, N, K, nullptr, ctx.sm_count, st);
@@ -1474,7 +1503,7 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
     fj.fork();
     // side: what the dX GEMM needs besides dH: W^T [K, M] and A [K, EXT] in bf16
     if (dX) {
-        if (!w4) lq_launch_dequant(w, t.wscr, LQ_BF16, M, 1, fj.side());
+        if (!w4 && !cached) lq_launch_dequant(w, t.wscr, LQ_BF16, M, 1, fj.side());
         if (!mirror) cast_pad(A, r, 1, t.pext, EXT, K, r, EXT, 1.f, fj.side());
     }
     fj.record(0);  // the caller's stream waits for this point just before the dX GEMM
@@ -1496,6 +1525,9 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
         fj.wait(0);
         if (w4) {
             lq_w4_gemm(w, 1, dY, M, t.ext_a, EXT, t.pext, EXT, EXT, dX, K, N, nullptr, st);
+        } else if (cached) {
+            Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
+            launch_gemm_pair<256, false, true>(a0, bmn, M, &a1, &b1, EXT, (__nv_bfloat16*)dX, K, N, K, nullptr, st);
         } else {
             Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
             main_gemm<__nv_bfloat16>(a0, b0, M, &a1, &b1, EXT, (__nv_bfloat16*)dX, K, N, K, nullptr, ctx.sm_count, st);

@@ -54,27 +54,35 @@ namespace {
 using namespace umma;
 using namespace lqgemm;
 
-constexpr int kW4Threads = 576;  // producer warp, MMA warp, 8 epilogue warps, 8 dequant warps
+constexpr int kGroupWarps = 2;   // warps per dequant group (four per group measured slower: 0.29 vs 0.26 ms)
+constexpr int kGroupThreads = 32 * kGroupWarps;
+constexpr int kChunks = 256 / kGroupThreads;  // 16-byte packed chunks per thread and k-block
+// producer warp, MMA warp, 8 epilogue warps, 4 dequant groups
+constexpr int kW4Threads = 64 + 256 + 4 * kGroupThreads;
 constexpr int BN = 256;          // columns of the pair tile; each CTA converts 128 of them
+constexpr int kGroups = 4;       // dequant groups (2 warps each) working on consecutive k-blocks
 
+// One ring: an operand stage holds this CTA's A tile and its dequantised B half.  The packed weight
+// bytes never pass through shared memory: the dequant threads load them from global memory straight
+// into registers, one block ahead (the operand reads of the tensor core, the A tiles' arrival and the
+// stores of the converted half already take most of the shared-memory bandwidth of a k-block time;
+// staging the packed bytes there too measured 0.27 ms against 0.22 ms for the same GEMM over a bf16
+// weight copy).  Four groups of two warps convert four consecutive k-blocks at once.
 struct W4Cfg {
     static constexpr uint32_t A_BYTES = BM * BK * 2;        // 16 KB: this CTA's 128 rows of A
     static constexpr uint32_t B_BYTES = (BN / 2) * BK * 2;  // 16 KB: this CTA's dequantised half of B
-    static constexpr uint32_t PK_BYTES = 4096;              // packed bytes behind one B half
-    static constexpr uint32_t SC_BYTES = 1024;              // up to 256 group scales behind one B half
-    static constexpr int STAGES = 5;
-    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES + PK_BYTES + SC_BYTES;
+    static constexpr int STAGES = 6;
     static constexpr uint32_t TMEM_COLS = 512;  // two 256-column accumulator stages
     static constexpr uint32_t STAGE_OUT = 8 * 2048;
-    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + STAGE_OUT + 1024 + 512;
+    static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + STAGE_OUT + 1024 + 512;
 };
+static_assert(W4Cfg::SMEM <= 232448, "shared memory budget of one CTA");
 
 struct W4Params {
     GemmParams g;
     const uint8_t* packed;  // [m_tiles][k_tiles][4096]
     const float* scales;    // [m_tiles][n_groups][128]
     int w_m_tiles, w_k_tiles, n_groups, gpt;  // gpt: scale groups per 64 d_in (1 or 2)
-    int debug;
 };
 
 // Address of the same shared-memory object in the cluster's CTA `rank`.
@@ -92,12 +100,13 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
 }
 // Bounded wait for roles that sit idle for most of a tile (the epilogue during the mainloop): sleeps
 // between polls so that the polling does not take issue slots from the conversion warps.
+template <int SLEEP_NS = 200>
 __device__ __forceinline__ bool mbar_wait_idle(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                                int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     for (uint32_t i = 1;; ++i) {
-        __nanosleep(200);
+        __nanosleep(SLEEP_NS);
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63u) == 0u) {
             if (*abort_flag) return false;
@@ -108,6 +117,15 @@ __device__ __forceinline__ bool mbar_wait_idle(uint32_t bar, uint32_t parity, vo
             }
         }
     }
+}
+
+// 16-byte read-only load that does not allocate in L1 (every packed byte is read once per output tile).
+__device__ __forceinline__ uint4 ld_nc_v4(const uint4* ptr) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(ptr));
+    return r;
 }
 
 // Eight packed elements (one word) -> eight bf16 (one 16-byte chunk of an operand row).
@@ -169,17 +187,14 @@ w4_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem_a + (size_t)STAGES * C::A_BYTES;
-    uint8_t* smem_pk = smem_b + (size_t)STAGES * C::B_BYTES;
-    uint8_t* smem_sc = smem_pk + (size_t)STAGES * C::PK_BYTES;
-    uint8_t* stage_out = smem_sc + (size_t)STAGES * C::SC_BYTES;  // 1024-aligned
+    uint8_t* stage_out = smem_b + (size_t)STAGES * C::B_BYTES;  // 1024-aligned
     uint64_t* bars = (uint64_t*)(stage_out + C::STAGE_OUT);
     uint64_t* full = bars;                 // leader: A bytes (and extension B bytes) of both CTAs
-    uint64_t* pfull = bars + STAGES;       // local: packed bytes + scales of this CTA
-    uint64_t* bfull = bars + 2 * STAGES;   // leader: 16 arrivals, the dequant warps of both CTAs
-    uint64_t* empty = bars + 3 * STAGES;   // both: the leader's multicast commit
-    uint64_t* tfull = bars + 4 * STAGES;
-    uint64_t* tempty = bars + 4 * STAGES + 2;
-    uint32_t* tmem_slot = (uint32_t*)(bars + 4 * STAGES + 4);
+    uint64_t* bfull = bars + STAGES;       // leader: 4 arrivals, the two warps of one dequant group in both CTAs
+    uint64_t* empty = bars + 2 * STAGES;   // both: the leader's multicast commit
+    uint64_t* tfull = bars + 3 * STAGES;
+    uint64_t* tempty = tfull + 2;
+    uint32_t* tmem_slot = (uint32_t*)(tempty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -189,8 +204,7 @@ w4_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(smem_u32(&full[s]), 1);
-            mbar_init(smem_u32(&pfull[s]), 1);
-            mbar_init(smem_u32(&bfull[s]), 16);
+            mbar_init(smem_u32(&bfull[s]), 2 * kGroupWarps);
             mbar_init(smem_u32(&empty[s]), 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -219,7 +233,10 @@ w4_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            // ---------------- producer (both CTAs) ----------------
+            // ---------------- producer (both CTAs): the A tiles, and the K extension's B tiles ----------------
+            // (the packed weight bytes are fetched by the dequant groups themselves: one thread issuing
+            // every copy of a k-block could not keep up with the MMA, above all in the backward, where a
+            // k-block takes up to seven copies)
             int s = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -230,7 +247,6 @@ w4_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
                 for (int kb = 0; kb < kb_total; ++kb) {
                     if (!mbar_wait(smem_u32(&empty[s]), phase ^ 1u, abort_flag, p.status, 61)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&full[s]);
-                    const uint32_t pbar = smem_u32(&pfull[s]);
                     const uint32_t sa = smem_u32(smem_a + (size_t)s * C::A_BYTES);
                     if (kb >= p.kb0) {
                         // K extension: both operands are bf16 tiles; nothing to convert
@@ -239,44 +255,9 @@ w4_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
                         tma_load_2d_pair(sa, &tmA1, bar, kc, arow);
                         tma_load_2d_pair(smem_u32(smem_b + (size_t)s * C::B_BYTES), &tmB1, bar, kc,
                                          n_tile * BN + (int)rank * (BN / 2));
-                        mbar_arrive(pbar);
                     } else {
                         if (leader) mbar_expect_tx(bar, 2 * C::A_BYTES);
                         tma_load_2d_pair(sa, &tmA0, bar, kb * BK, arow);
-                        const uint32_t spk = smem_u32(smem_pk + (size_t)s * C::PK_BYTES);
-                        const uint32_t ssc = smem_u32(smem_sc + (size_t)s * C::SC_BYTES);
-                        if (!TRANS) {
-                            // this CTA's 128 output columns are one packed tile row block: tile (mt, kb)
-                            const int mt = n_tile * 2 + (int)rank;
-                            if (mt < wp.w_m_tiles) {
-                                const uint32_t scb = (uint32_t)wp.gpt * 512u;
-                                mbar_expect_tx(pbar, C::PK_BYTES + scb);
-                                bulk_load(spk, wp.packed + ((size_t)mt * wp.w_k_tiles + kb) * 4096, C::PK_BYTES, pbar);
-                                bulk_load(ssc, wp.scales + ((size_t)mt * wp.n_groups + (size_t)kb * wp.gpt) * 128, scb, pbar);
-                            } else {
-                                mbar_arrive(pbar);  // columns past d_out: whatever is converted is clipped by the store
-                            }
-                        } else {
-                            // 64 reduction rows = the upper or lower half of packed m-tile kb / 2; this CTA's 128
-                            // output columns = the two k-tiles kt0, kt0 + 1
-                            const int mt = kb >> 1, hrow = (kb & 1) * 64;
-                            const int kt0 = n_tile * 4 + (int)rank * 2;
-                            const int nk = min(2, wp.w_k_tiles - kt0);  // k-tiles that exist (<= 0: all clipped)
-                            if (nk > 0) {
-                                mbar_expect_tx(pbar, (uint32_t)nk * (2048u + (uint32_t)wp.gpt * 256u));
-                                for (int c = 0; c < nk; ++c) {
-                                    const int kt = kt0 + c;
-                                    bulk_load(spk + c * 2048, wp.packed + ((size_t)mt * wp.w_k_tiles + kt) * 4096 + hrow * 32,
-                                              2048, pbar);
-                                    for (int h = 0; h < wp.gpt; ++h)  // scale slot: [half][chunk][64 rows]
-                                        bulk_load(ssc + (uint32_t)(h * 128 + c * 64) * 4u,
-                                                  wp.scales + ((size_t)mt * wp.n_groups + (size_t)kt * wp.gpt + h) * 128 + hrow,
-                                                  256, pbar);
-                                }
-                            } else {
-                                mbar_arrive(pbar);
-                            }
-                        }
                     }
                     if (++s == STAGES) { s = 0; phase ^= 1u; }
                 }
@@ -328,35 +309,100 @@ w4_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
             }
         }
     } else if (warp >= 10) {
-        // ---------------- dequant (warps 10..17 of both CTAs) ----------------
-        const int dt = threadIdx.x - 320;          // 0..255
-        const int row = dt >> 1, half = dt & 1;    // operand row (0..127), 32-element half of it
+        // ---------------- dequant (warps 10..17 of both CTAs): four groups of two warps ----------------
+        // Group g converts the k-blocks whose running index is g modulo 4, so four consecutive k-blocks
+        // are in conversion at once and a group's fixed costs (the barrier wait, the proxy fence, the
+        // arrival) are paid once per 8192 weights.  A thread owns four 16-byte chunks of the block's
+        // packed bytes (chunk c = gt + 64 i: operand row c >> 1, 32-element half c & 1) and their row
+        // scales; it loads the NEXT block's chunks from global memory before converting the current one.
+        const int grp = (warp - 10) / kGroupWarps;
+        const int gt = (threadIdx.x - 320) % kGroupThreads;  // thread within the group
+        const int half = gt & 1;
         const uint32_t bfull_leader = map_to_cta(smem_u32(&bfull[0]), 0);  // the leader's barriers (own, if leader)
-        const int sc_idx = (wp.gpt == 2 ? half * 128 : 0) + row;
-        int s = 0;
-        uint32_t phase = 0;
-        bool ok = true;
-        for (int item = cid; ok && item < num_items; item += ncl) {
-            for (int kb = 0; kb < kb_total; ++kb) {
-                if (!mbar_wait(smem_u32(&pfull[s]), phase, abort_flag, p.status, 65)) { ok = false; break; }
-                if (!mbar_wait(smem_u32(&empty[s]), phase ^ 1u, abort_flag, p.status, 66)) { ok = false; break; }
-                if (kb < p.kb0) {
-                    const uint4 v = *((const uint4*)(smem_pk + (size_t)s * C::PK_BYTES) + dt);
-                    const float sc = *((const float*)(smem_sc + (size_t)s * C::SC_BYTES) + sc_idx);
-                    const ScalePair sp = make_scale(sc);
-                    uint8_t* brow = smem_b + (size_t)s * C::B_BYTES + row * 128;
-                    const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+
+        // Loads the chunks behind k-block `kb` of output-column tile `n_tile`; false when that block has
+        // no packed bytes (K extension, or columns past the weight's extent: those are clipped by the store).
+        auto fetch = [&](int n_tile, int kb, uint4 (&v)[kChunks], float (&sc)[kChunks]) -> bool {
+            if (kb >= p.kb0) return false;
+            if (!TRANS) {
+                const int mt = n_tile * 2 + (int)rank;  // this CTA's 128 output columns = packed tile row block mt
+                if (mt >= wp.w_m_tiles) return false;
+                const uint4* tile = (const uint4*)(wp.packed + ((size_t)mt * wp.w_k_tiles + kb) * 4096);
+                const float* scl = wp.scales + ((size_t)mt * wp.n_groups + (size_t)kb * wp.gpt + (wp.gpt == 2 ? half : 0)) * 128;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int chunk = (half * 4 + i) ^ (row & 7);  // 128-byte swizzle of the operand layout
-                        *(uint4*)(brow + chunk * 16) = convert_word<MODE>(words[i], sp);
-                    }
-                    fence_proxy_async_smem();  // this lane's stores are visible to the tensor core's reads
+                for (int i = 0; i < kChunks; ++i) {
+                    v[i] = ld_nc_v4(tile + gt + kGroupThreads * i);
+                    sc[i] = __ldg(scl + (gt >> 1) + (kGroupThreads / 2) * i);
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive_remote(bfull_leader + (uint32_t)s * 8u);
-                if (++s == STAGES) { s = 0; phase ^= 1u; }
+                return true;
             }
+            // backward: 64 reduction rows = the upper or lower half of packed m-tile kb / 2; this CTA's 128
+            // output columns = the two k-tiles kt0, kt0 + 1 (chunks 0..127 and 128..255)
+            const int mt = kb >> 1, hrow = (kb & 1) * 64;
+            const int kt0 = n_tile * 4 + (int)rank * 2;
+            if (kt0 >= wp.w_k_tiles) return false;
+#pragma unroll
+            for (int i = 0; i < kChunks; ++i) {
+                const int ch = gt + kGroupThreads * i;  // chunk of the 256: k-tile ch >> 7, chunk ch & 127 of its half tile
+                const int kt = min(kt0 + (ch >> 7), wp.w_k_tiles - 1);  // a missing second k-tile: its columns are clipped
+                const uint4* tile = (const uint4*)(wp.packed + ((size_t)mt * wp.w_k_tiles + kt) * 4096 + hrow * 32);
+                v[i] = ld_nc_v4(tile + (ch & 127));
+                sc[i] = __ldg(wp.scales + ((size_t)mt * wp.n_groups + (size_t)kt * wp.gpt + (wp.gpt == 2 ? half : 0)) * 128 +
+                              hrow + ((ch & 127) >> 1));
+            }
+            return true;
+        };
+        // position of the group's current block in this CTA's sequence of (item, k-block)
+        auto advance = [&](int& item, int& kb, int by) {
+            kb += by;
+            while (item < num_items && kb >= kb_total) { kb -= kb_total; item += ncl; }
+        };
+        auto tile_of = [&](int item) {
+            int m_tile, n_tile, z;
+            item_coords(p, item, m_tile, n_tile, z);
+            return n_tile;
+        };
+        int item = cid, kb = 0;
+        advance(item, kb, grp);
+        uint4 v[kChunks], vn[kChunks];
+        float sc[kChunks], scn[kChunks];
+        bool have = item < num_items && fetch(tile_of(item), kb, v, sc);
+        uint32_t kbi = (uint32_t)grp;
+        bool ok = true;
+        while (ok && item < num_items) {
+            const int s = (int)(kbi % STAGES);
+            const uint32_t phase = (kbi / STAGES) & 1u;
+            int item1 = item, kb1 = kb;
+            advance(item1, kb1, kGroups);
+            const bool have1 = item1 < num_items && fetch(tile_of(item1), kb1, vn, scn);  // in flight during the conversion
+            if (!mbar_wait(smem_u32(&empty[s]), phase ^ 1u, abort_flag, p.status, 66)) { ok = false; break; }
+            if (have) {
+                uint8_t* bst = smem_b + (size_t)s * C::B_BYTES;
+#pragma unroll
+                for (int i = 0; i < kChunks; ++i) {
+                    const int row = (gt >> 1) + (kGroupThreads / 2) * i;
+                    const ScalePair sp = make_scale(sc[i]);
+                    const uint32_t words[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+                    uint8_t* brow = bst + row * 128;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int chunk = (half * 4 + q) ^ (row & 7);  // 128-byte swizzle of the operand layout
+                        *(uint4*)(brow + chunk * 16) = convert_word<MODE>(words[q], sp);
+                    }
+                }
+                fence_proxy_async_smem();  // this lane's stores are visible to the tensor core's reads
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(bfull_leader + (uint32_t)s * 8u);
+            item = item1;
+            kb = kb1;
+            have = have1;
+#pragma unroll
+            for (int i = 0; i < kChunks; ++i) {
+                v[i] = vn[i];
+                sc[i] = scn[i];
+            }
+            kbi += kGroups;
         }
     } else {
         // ---------------- epilogue (warps 2..9 of both CTAs, each its own 128 rows) ----------------
@@ -368,9 +414,7 @@ w4_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
         for (int item = cid; ok && item < num_items; item += ncl) {
             int m_tile, n_tile, z;
             item_coords(p, item, m_tile, n_tile, z);
-            const bool ready = (wp.debug & 16) ? mbar_wait(smem_u32(&tfull[acc]), acc_phase, abort_flag, p.status, 67)
-                                               : mbar_wait_idle(smem_u32(&tfull[acc]), acc_phase, abort_flag, p.status, 67);
-            if (!ready) { ok = false; break; }
+            if (!mbar_wait_idle(smem_u32(&tfull[acc]), acc_phase, abort_flag, p.status, 67)) { ok = false; break; }
             tc_fence_after();
             const int row0 = m_tile * 256 + (int)rank * BM + quarter * 32;
 #pragma unroll 1
@@ -436,9 +480,8 @@ int env_int(const char* name, int dflt) {
 }
 
 // Run-time switches (initial values from the environment, changed through lq_option_set).
-std::atomic<int> g_w4_on{env_int("LQ_W4", 1)};
+std::atomic<int> g_w4_on{env_int("LQ_W4", 0)};
 std::atomic<int> g_w4_exact{env_int("LQ_W4_EXACT", 1)};
-std::atomic<int> g_w4_debug{0};
 
 template <bool TRANS, int MODE>
 void launch_w4(const lq_weight* w, const void* A0, int64_t lda, const void* a1, int64_t lda1, const void* b1,
@@ -473,7 +516,6 @@ void launch_w4(const lq_weight* w, const void* A0, int64_t lda, const void* a1, 
     wp.w_k_tiles = (int)w->k_tiles;
     wp.n_groups = (int)w->n_groups;
     wp.gpt = 64 / w->group;
-    wp.debug = g_w4_debug.load();
     auto kern = w4_gemm2_kernel<TRANS, MODE>;
     LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
     static std::mutex mu;
@@ -507,7 +549,6 @@ void launch_w4(const lq_weight* w, const void* A0, int64_t lda, const void* a1, 
 bool lq_w4_option_set(const char* name, int value) {
     if (std::strcmp(name, "w4") == 0) { g_w4_on = value; return true; }
     if (std::strcmp(name, "w4_exact") == 0) { g_w4_exact = value; return true; }
-    if (std::strcmp(name, "w4_debug") == 0) { g_w4_debug = value; return true; }
     return false;
 }
 

@@ -110,7 +110,9 @@ class BlockStack(nn.Module):
     """`n_blocks` double-stream blocks with one LoRA adapter set over every linear."""
 
     def __init__(self, n_blocks: int, cfg: BlockConfig, rank: int, alpha: float, device, seed: int = 5,
-                 dtype: torch.dtype = torch.bfloat16):
+                 dtype: torch.dtype = torch.bfloat16, weight_copies: bool = False):
+        """`weight_copies`: keep a resident bf16 copy of every frozen weight (2 bytes per element beside
+        the packed 0.5), so that no call dequantises — the memory-for-time trade a 180 GB GPU allows."""
         super().__init__()
         gen = torch.Generator(device=device).manual_seed(seed)
         self.cfg, self.dtype = cfg, dtype
@@ -125,6 +127,9 @@ class BlockStack(nn.Module):
                 d.lora_b.copy_(torch.randn(d.lora_b.shape, generator=g2, device=device) * 0.01)
         for blk in self.blocks:
             blk.adapters = self.adapters
+            if weight_copies:
+                for base in blk.bases.values():
+                    base.inner.weight.attach_bf16_copy()
         self.flat = FlatAdapters(self.adapters, device)
         # slice of the flat buffers that holds block i's adapters (registration order = block order)
         per_block = 2 * len(DoubleStreamBlock.STREAMS) * len(DoubleStreamBlock.LINEARS)

@@ -110,6 +110,24 @@ class QuantWeight:
             L.check(L.lib().lq_weight_set_bias(self._h, b.data_ptr(), _stream_ptr(self.device)))
             torch.cuda.current_stream(self.device).synchronize()  # b may be a temporary
 
+    def attach_bf16_copy(self, buffer: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Keeps a resident bf16 `[d_out, d_in]` copy of the dequantised weight (`lq_weight_attach_bf16_copy`):
+        bf16 calls at >= 65 tokens then run no dequantisation pass.  `buffer` (bf16, `d_out * d_in`
+        elements) may be supplied to reuse memory, e.g. one block's worth under block checkpointing."""
+        n = self.d_out * self.d_in
+        if buffer is None:
+            buffer = torch.empty(n, dtype=torch.bfloat16, device=self.device)
+        if buffer.dtype != torch.bfloat16 or buffer.numel() < n or not buffer.is_contiguous():
+            raise ValueError("bf16 copy buffer must be a contiguous bf16 tensor of at least d_out * d_in elements")
+        with torch.cuda.device(self.device):
+            L.check(L.lib().lq_weight_attach_bf16_copy(self._h, buffer.data_ptr(), _stream_ptr(self.device)))
+        self._bf16_copy = buffer  # keeps the memory alive while attached
+        return buffer
+
+    def detach_bf16_copy(self) -> None:
+        L.check(L.lib().lq_weight_attach_bf16_copy(self._h, None, None))
+        self._bf16_copy = None
+
     def prepare_fp8_backward(self) -> None:
         """Builds the transposed e4m3 copy the native-fp8 backward reads, at load time, so the
         step loop stays allocation-free (otherwise the first such backward builds it)."""

@@ -161,7 +161,7 @@ def test_lora_toy_twenty_sgd_steps_on_the_gpu(golden_dir):
 
     losses = []
     for _ in range(hp["steps"]):
-        y = _LoraLinearFn.apply(xd, A, B, wq, hp["alpha"] / hp["rank"])[:, :3]
+        y = _LoraLinearFn.apply(xd, A, B, wq, hp["alpha"] / hp["rank"], None)[:, :3]
         loss = ((y - td) ** 2).mean()
         losses.append(float(loss))
         A.grad = B.grad = None

@@ -32,9 +32,13 @@ def set_option(name, value):
 
 
 @pytest.fixture(autouse=True)
-def restore_options():
-    yield
+def w4_on_for_these_tests():
+    """The in-mainloop path is an option (off by default: the scratch-copy path measured faster at
+    every size tried); these tests switch it on and restore the defaults afterwards."""
     set_option("w4", 1)
+    set_option("w4_exact", 1)
+    yield
+    set_option("w4", 0)
     set_option("w4_exact", 1)
 
 
