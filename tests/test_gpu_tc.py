@@ -191,3 +191,23 @@ def test_split_gemm_rejects_more_splits_than_k_blocks():
                               part.data_ptr(), None, st)
     assert rc == L.LQ_ERR_INVALID
     assert b"splits must not exceed" in L.lib().lq_last_error()
+
+
+@pytest.mark.parametrize("n,k,m", [(20480, 128, 256), (19200, 192, 520)])
+def test_more_tiles_than_cta_pairs_with_a_thin_last_round(n, k, m):
+    """More 256 x 256 tiles than resident CTA pairs, the last round filling only a few of them: the
+    persistent grid wraps around; every output element must be written exactly once and correctly."""
+    from loractl_b200 import quant as Q
+
+    wq, dq, x, dy, a, b = oracle_case(n, k, m, 8, "int4")
+    xd, dyd, ad, bd = dev(x, torch.bfloat16), dev(dy, torch.bfloat16), dev(a), dev(b)
+    y, h = Q.linear_fwd_raw(wq, xd, ad, bd, 1.5)
+    dx, da, db = Q.linear_bwd_raw(wq, dyd, xd, h, ad, bd, 1.5)
+    lb().check_device_status()
+    assert torch.isfinite(y).all() and torch.isfinite(dx).all()
+    oy, _ = O.lora_linear_fwd(x, dq, a, b, 1.5)
+    odx, oda, odb = O.lora_linear_bwd(dy, x, dq, a, b, 1.5)
+    assert reldev(host(y), oy) <= 6e-3 and reldev(host(dx), odx) <= 6e-3
+    assert reldev(host(da), oda) <= 8e-3 and reldev(host(db), odb) <= 8e-3
+    y2, _ = Q.linear_fwd_raw(wq, xd, ad, bd, 1.5)
+    assert torch.equal(y, y2)
