@@ -574,7 +574,9 @@ def run_ours(args):
                 "hbm_peak_gbs": hbm_peak,
                 "sites": {key: {"stream_bytes_per_site": v["stream_bytes_per_site"], "distinct_sites": v["sites"],
                                 "by_tokens": {t: {"site_us": d["site_us"], "gbs": d["site_stream_gbs"],
-                                                  "frac": d["frac_of_hbm"]} for t, d in v["by_tokens"].items()}}
+                                                  "frac": d["frac_of_hbm"], "grouped4_site_us": d["grouped4_site_us"],
+                                                  "grouped4_frac": d["grouped4_frac_of_hbm"]}
+                                              for t, d in v["by_tokens"].items()}}
                           for key, v in sres.items()},
             }
         # `sustained`: one region of at least two seconds, the regime a training loop runs in (the SM clock
@@ -751,30 +753,45 @@ def measure_stream(dev, reps: int, token_counts=(1, 8, 16, 64)):
             lib.lq_profile_enable(0)
             kinds = {lib.lq_profile_kind_name(i).decode(): (ms_kind[i], int(cnt_kind[i])) for i in range(nk)}
             fused_ms = kinds["gemm_main"][0] / max(kinds["gemm_main"][1], 1)
-            # whole-site time, graph replay
-            graph = torch.cuda.CUDAGraph()
-            side = torch.cuda.Stream(dev)
-            side.wait_stream(torch.cuda.current_stream(dev))
-            with torch.cuda.stream(side):
-                chain()
-                with torch.cuda.graph(graph, stream=side):
-                    chain()
-            torch.cuda.current_stream(dev).wait_stream(side)
-            for _ in range(3):
-                graph.replay()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(reps):
-                graph.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            site_ms = e0.elapsed_time(e1) / (reps * sites)
-            lb.check_device_status(dev)
-            del graph
+            # whole-site time, graph replay; int4 sites also as groups of four sites that share X
+            # (one launch pair per group: `lq_linear_fwd_grouped`)
+            def chain_grouped():
+                y = None
+                for i0 in range(0, len(weights), 4):
+                    outs = Q.linear_fwd_grouped_raw([(wq, a, b, s) for wq in weights[i0:i0 + 4]], x, want_h=False)
+                    y = outs[-1][0]
+                return y
+
+            def replay_time(fn):
+                for _ in range(2):
+                    fn()
+                graph = torch.cuda.CUDAGraph()
+                side = torch.cuda.Stream(dev)
+                side.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(side):
+                    fn()
+                    with torch.cuda.graph(graph, stream=side):
+                        fn()
+                torch.cuda.current_stream(dev).wait_stream(side)
+                for _ in range(3):
+                    graph.replay()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps):
+                    graph.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                lb.check_device_status(dev)
+                return e0.elapsed_time(e1) / (reps * sites)
+
+            site_ms = replay_time(chain)
+            grouped_ms = replay_time(chain_grouped) if (scheme == "int4" and n <= 16) else None
             results[str(n)] = {
                 "site_us": site_ms * 1e3, "site_stream_gbs": stream_bytes / (site_ms * 1e-3) / 1e9,
                 "frac_of_hbm": stream_bytes / (site_ms * 1e-3) / 1e9 / hbm,
+                "grouped4_site_us": grouped_ms * 1e3 if grouped_ms else None,
+                "grouped4_frac_of_hbm": stream_bytes / (grouped_ms * 1e-3) / 1e9 / hbm if grouped_ms else None,
                 "fused_kernel_us": fused_ms * 1e3,
                 "fused_kernel_stream_gbs": stream_bytes / (fused_ms * 1e-3) / 1e9,
                 "by_kernel_us": {kk: v[0] / max(v[1], 1) * 1e3 for kk, v in kinds.items() if v[1]},

@@ -221,6 +221,27 @@ size_t lq_lora_mirror_bytes(int64_t d_in, int64_t d_out, int rank);
 int lq_lora_mirror_update(const float* A, const float* B, int64_t d_in, int64_t d_out, int rank,
                           void* mirror, void* stream);
 
+/* Several sites that read the SAME activation — the reference calls `site()` three times on one x
+ * for wq / wk / wv and twice for gate / up (crates/loractl-core/src/mmdit.rs:599-610,701-706) — in
+ * one call.  Semantics per site are exactly lq_linear_fwd's (Y_i = X . dequant(W_i)^T + bias_i +
+ * s_i (X . A_i) . B_i, H_i = X . A_i).  With int4 weights of one d_in and quant block at <= 16 tokens
+ * (LQ_BF16) the whole group is ONE launch of the packed-weight-stream kernel over the concatenated
+ * work list of the sites plus one finalize launch, so launch ramp and tail are paid once per group;
+ * any other request runs the sites one after the other through lq_linear_fwd.  At most 4 sites take
+ * the one-launch path.  `workspace`: at least lq_linear_grouped_workspace_bytes() bytes. */
+typedef struct lq_group_site {
+    const lq_weight_t* w;
+    const float* A;      /* [d_in, rank] f32, NULL when rank == 0 */
+    const float* B;      /* [rank, d_out] f32 */
+    int32_t rank;
+    float scaling;
+    void* Y;             /* [n_tokens, d_out] */
+    float* H_out;        /* [n_tokens, rank] f32, may be NULL */
+} lq_group_site;
+size_t lq_linear_grouped_workspace_bytes(const lq_group_site* sites, int n_sites, int64_t n_tokens, int dtype);
+int lq_linear_fwd_grouped(const lq_group_site* sites, int n_sites, const void* X, int64_t n_tokens, int dtype,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
 /* Builds, once, the transposed copy of a scaled-fp8 weight that the LQ_BF16_W8A8 backward reads
  * ([d_in, d_out] e4m3 bytes, +1 byte per element of resident memory).  Optional: the first
  * LQ_BF16_W8A8 backward builds it on demand (one cudaMalloc); call this at load time to keep the

@@ -25,6 +25,12 @@ class LqError(RuntimeError):
         self.message = message
 
 
+class GroupSite(C.Structure):
+    """`lq_group_site` of include/loractl_b200.h."""
+    _fields_ = [("w", C.c_void_p), ("A", C.c_void_p), ("B", C.c_void_p), ("rank", C.c_int32), ("scaling", C.c_float),
+                ("Y", C.c_void_p), ("H_out", C.c_void_p)]
+
+
 class WeightInfo(C.Structure):
     _fields_ = [
         ("d_out", C.c_int64), ("d_in", C.c_int64), ("scheme", C.c_int32), ("group", C.c_int32),
@@ -57,6 +63,8 @@ SIGNATURES = {
     "lq_weight_attach_bf16_copy": (_I, [_P, _P, _P]),
     "lq_lora_mirror_bytes": (_SZ, [_I64, _I64, _I]),
     "lq_lora_mirror_update": (_I, [_P, _P, _I64, _I64, _I, _P, _P]),
+    "lq_linear_grouped_workspace_bytes": (_SZ, [C.POINTER(GroupSite), _I, _I64, _I]),
+    "lq_linear_fwd_grouped": (_I, [C.POINTER(GroupSite), _I, _P, _I64, _I, _P, _SZ, _P]),
     "lq_weight_prepare_fp8_backward": (_I, [_P, _P]),
     "lq_grad_nonfinite_flag": (_I, [_P, _I64, _P, _P]),
     "lq_adamw_step": (_I, [_P, _P, _P, _P, _I64, _F, _F, _F, _F, _F, _I64, _F, _P, _P]),

@@ -514,6 +514,40 @@ int lq_linear_bwd(const lq_weight_t* w, const void* dY, const void* X, const flo
     });
 }
 
+size_t lq_linear_grouped_workspace_bytes(const lq_group_site* sites, int n_sites, int64_t n_tokens, int dtype) {
+    if (!sites || n_sites < 1 || n_tokens < 0) return 0;
+    if (dtype == LQ_BF16 && lq_fused_group_supported(sites, n_sites, n_tokens))
+        return align256(lq_fused_group_workspace_bytes(sites, n_sites, n_tokens)) + 256;
+    size_t need = 0;
+    for (int i = 0; i < n_sites; ++i) need = std::max(need, lq_linear_workspace_bytes(sites[i].w, n_tokens, sites[i].rank, dtype));
+    return need;
+}
+
+int lq_linear_fwd_grouped(const lq_group_site* sites, int n_sites, const void* X, int64_t n_tokens, int dtype,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = guarded([&] {
+        LQ_CHECK_ARG(sites != nullptr && n_sites >= 1, "no sites");
+        for (int i = 0; i < n_sites; ++i) {
+            check_call(sites[i].w, n_tokens, dtype, sites[i].A, sites[i].B, sites[i].rank);
+            LQ_CHECK_ARG(sites[i].w->K == sites[0].w->K, "the sites of a group share X: their d_in must agree");
+        }
+        LQ_CHECK_ARG(n_tokens == 0 || X != nullptr, "X pointer is NULL");
+    });
+    if (rc != LQ_OK || n_tokens == 0) return rc;
+    if (dtype == LQ_BF16 && lq_fused_group_supported(sites, n_sites, n_tokens)) {
+        return guarded([&] {
+            DeviceGuard dg(sites[0].w->device);
+            lq_fused_fwd_grouped(sites, n_sites, X, n_tokens, workspace, workspace_bytes, (cudaStream_t)stream);
+        });
+    }
+    for (int i = 0; i < n_sites; ++i) {  // one after the other; the stream orders their use of the workspace
+        rc = lq_linear_fwd(sites[i].w, X, n_tokens, dtype, sites[i].A, sites[i].B, sites[i].rank, sites[i].scaling,
+                           sites[i].Y, sites[i].H_out, workspace, workspace_bytes, stream, nullptr);
+        if (rc != LQ_OK) return rc;
+    }
+    return LQ_OK;
+}
+
 int lq_weight_prepare_fp8_backward(const lq_weight_t* w, void* stream) {
     return guarded([&] {
         LQ_CHECK_ARG(w != nullptr, "weight handle is NULL");

@@ -57,6 +57,12 @@ size_t lq_fused_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank);
 void lq_fused_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, const float* B, int r, float s,
                   void* Y, float* H_out, void* ws, size_t ws_bytes, cudaStream_t st);
 
+// A group of sites that share X, as one launch of the <= 16-token stream kernel plus one finalize.
+bool lq_fused_group_supported(const lq_group_site* sites, int n_sites, int64_t n_tokens);
+size_t lq_fused_group_workspace_bytes(const lq_group_site* sites, int n_sites, int64_t n_tokens);
+void lq_fused_fwd_grouped(const lq_group_site* sites, int n_sites, const void* X, int64_t N, void* ws, size_t ws_bytes,
+                          cudaStream_t st);
+
 // Native fp8 compute (scaled-fp8 weights only): e4m3 weights straight from HBM x per-token e4m3
 // activations on tcgen05 kind::f8f6f4, scales applied in the epilogue, LoRA extension kept in bf16.
 bool lq_w8a8_supported(const lq_weight* w, int64_t n_tokens, int rank);

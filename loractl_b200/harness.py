@@ -30,7 +30,7 @@ from . import dp
 from .adapters import LoraAdapters, LoraConfig, LoraSite, TargetSpec, build_adapters
 from .block_ckpt import checkpointed_step
 from .block_ops import gated_residual, modulated_layer_norm
-from .linear import BaseLinear, QuantLinear, site
+from .linear import BaseLinear, QuantLinear, site, site_group
 from .optim import AdamW, DynamicLossScale, FlatAdapters, nonfinite_flag
 from .quant import quantize_linear_weight
 
@@ -87,8 +87,10 @@ class DoubleStreamBlock(nn.Module):
         xs = {"img": state[:, :li], "txt": state[:, li:]}
         cond = F.silu(self.cond.to(state.dtype))
         mods, qkvs = {}, {}
-        for s in self.STREAMS:
-            mods[s] = self._lin(s, "mod", cond).unsqueeze(1).chunk(6, dim=-1)
+        # both streams' modulation projections read the same conditioning vector: one grouped call
+        mod_out = site_group(self.adapters, [(self.path(s, "mod"), self.bases[f"{s}_mod"]) for s in self.STREAMS], cond)
+        for s, mo in zip(self.STREAMS, mod_out):
+            mods[s] = mo.unsqueeze(1).chunk(6, dim=-1)
             shift, scale = mods[s][0], mods[s][1]
             xn = modulated_layer_norm(xs[s], shift, scale)  # LN(x) * (1 + scale) + shift, one kernel
             qkvs[s] = self._lin(s, "qkv", xn).view(b, -1, 3, cfg.heads, h // cfg.heads)

@@ -126,6 +126,68 @@ def _fused(wq: Q.QuantWeight, x: torch.Tensor, delta: Optional[LoraDelta]) -> to
     return y.reshape(*lead, wq.d_out)
 
 
+class _GroupedLoraLinearFn(torch.autograd.Function):
+    """Several LoRA'd quantized sites on the same input: one grouped forward; the backward runs each
+    site's own `lq_linear_bwd` (dX contributions add up, as autograd would add them)."""
+
+    @staticmethod
+    def forward(ctx, x2, meta, *factors):
+        sites = []
+        for i, (wq, scaling, has_delta, _) in enumerate(meta):
+            a, b = (factors[2 * i], factors[2 * i + 1]) if has_delta else (None, None)
+            sites.append((wq, a, b, scaling))
+        outs = Q.linear_fwd_grouped_raw(sites, x2)
+        ctx.meta = meta
+        ctx.save_for_backward(x2, *[h if h is not None else x2.new_empty(0) for _, h in outs], *factors)
+        return tuple(y for y, _ in outs)
+
+    @staticmethod
+    def backward(ctx, *dys):
+        n = len(ctx.meta)
+        x2 = ctx.saved_tensors[0]
+        hs = ctx.saved_tensors[1:1 + n]
+        factors = ctx.saved_tensors[1 + n:]
+        dx_total, grads = None, []
+        for i, (wq, scaling, has_delta, mirror) in enumerate(ctx.meta):
+            a, b = (factors[2 * i], factors[2 * i + 1]) if has_delta else (None, None)
+            h = hs[i] if has_delta else None
+            need_dx = ctx.needs_input_grad[0]
+            dx, da, db = Q.linear_bwd_raw(wq, dys[i].contiguous(), x2, h, a, b, scaling, need_dx=need_dx,
+                                          need_da=has_delta and ctx.needs_input_grad[2 + 2 * i],
+                                          need_db=has_delta and ctx.needs_input_grad[3 + 2 * i], mirror=mirror)
+            if dx is not None:
+                dx_total = dx if dx_total is None else dx_total + dx
+            grads += [da, db]
+        return (dx_total, None, *grads)
+
+
+def site_group(adapters: Optional[LoraAdapters], sites, x: torch.Tensor):
+    """`site()` for several (path, base) pairs that read the SAME `x` — wq / wk / wv and gate / up in
+    the reference (crates/loractl-core/src/mmdit.rs:599-610,701-706).  Quantized bases go through one
+    grouped call; anything else falls back to `site()` one by one.  Returns the outputs in order."""
+    deltas = [adapters.get(path) if adapters is not None else None for path, _ in sites]
+    if not all(base.is_quant for _, base in sites) or not x.is_cuda:
+        return [apply_site(base, d, x) for (_, base), d in zip(sites, deltas)]
+    d_in = sites[0][1].d_in
+    if x.shape[-1] != d_in or any(base.d_in != d_in for _, base in sites):
+        raise ValueError("the sites of a group share x: their d_in must agree")
+    for d in deltas:
+        if d is not None and d.dropout > 0.0 and d.training:
+            raise RuntimeError("lora.dropout > 0 is not supported on a quantized site of the b200 backend")
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, d_in).contiguous()
+    meta, factors = [], []
+    for (_, base), d in zip(sites, deltas):
+        mirror = d.operand_mirror() if (d is not None and x2.dtype == torch.bfloat16) else None
+        meta.append((base.inner.weight, d.scaling if d is not None else 1.0, d is not None, mirror))
+        if d is not None:
+            factors += [d.lora_a, d.lora_b]
+        else:  # placeholders keep the argument positions regular
+            factors += [x2.new_empty(0), x2.new_empty(0)]
+    ys = _GroupedLoraLinearFn.apply(x2, tuple(meta), *factors)
+    return [y.reshape(*lead, base.d_out) for y, (_, base) in zip(ys, sites)]
+
+
 def apply_site(base: BaseLinear, delta: Optional[LoraDelta], x: torch.Tensor) -> torch.Tensor:
     if base.is_quant:
         return _fused(base.inner.weight, x, delta)

@@ -294,6 +294,40 @@ def linear_fwd_raw(wq: QuantWeight, x2: torch.Tensor, a: Optional[torch.Tensor],
     return y, h
 
 
+def linear_fwd_grouped_raw(sites, x2: torch.Tensor, want_h: bool = True):
+    """`lq_linear_fwd_grouped`: several sites that read the same flattened activation `x2`.
+    `sites` is a list of `(wq, a, b, scaling)` (a, b None for a base-only site).  Returns a list of
+    `(y, h)`.  At <= 16 bf16 tokens with int4 weights of one width the group is one launch pair."""
+    _require_cuda(x2, "x")
+    n = x2.shape[0]
+    dt = _dtype_code(x2)
+    arr = (L.GroupSite * len(sites))()
+    outs, keep = [], []
+    for i, (wq, a, b, scaling) in enumerate(sites):
+        rank = 0 if a is None else a.shape[1]
+        y = torch.empty((n, wq.d_out), dtype=x2.dtype, device=x2.device)
+        h = torch.empty((n, rank), dtype=torch.float32, device=x2.device) if (rank and want_h) else None
+        arr[i].w = wq.handle
+        arr[i].A = a.data_ptr() if rank else None
+        arr[i].B = b.data_ptr() if rank else None
+        arr[i].rank = rank
+        arr[i].scaling = float(scaling)
+        arr[i].Y = y.data_ptr()
+        arr[i].H_out = h.data_ptr() if h is not None else None
+        outs.append((y, h))
+        keep.append((a, b))
+    with torch.cuda.device(x2.device):
+        need = int(L.lib().lq_linear_grouped_workspace_bytes(arr, len(sites), n, dt))
+        key = (x2.device.index, torch.cuda.current_stream(x2.device).cuda_stream)
+        ws = _workspaces.get(key)
+        if ws is None or ws.numel() < need + 256:
+            ws = torch.empty(need + 512, dtype=torch.uint8, device=x2.device)
+            _workspaces[key] = ws
+        wp, wn = _aligned(ws)
+        L.check(L.lib().lq_linear_fwd_grouped(arr, len(sites), x2.data_ptr(), n, dt, wp, wn, _stream_ptr(x2.device)))
+    return outs
+
+
 def linear_bwd_raw(wq: QuantWeight, dy2: torch.Tensor, x2: Optional[torch.Tensor], h: Optional[torch.Tensor],
                    a: Optional[torch.Tensor], b: Optional[torch.Tensor], scaling: float,
                    need_dx: bool = True, need_da: bool = True, need_db: bool = True,
