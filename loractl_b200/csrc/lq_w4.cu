@@ -12,11 +12,14 @@
 // even CTA issues tcgen05.mma.cta_group::2 with M = 256, and each CTA's TMEM receives its own 128
 // accumulator rows.  What differs is where the B half comes from:
 //
-//   warp 0       producer: TMA tile of A (cp.async.bulk.tensor, no multicast) + untiled bulk copies
-//                of this CTA's packed weight bytes and their scales, per 64-deep k-block
-//   warps 10-17  dequant: packed words -> bf16 in the 128-byte-swizzled operand layout the MMA
-//                descriptor expects (generic-proxy stores, fence.proxy.async, one arrival per warp on
-//                the leader CTA's barrier)
+//   warp 0       producer: TMA tile of A (cp.async.bulk.tensor, no multicast), and the plain bf16
+//                B tiles of the LoRA extension blocks
+//   warps 10-17  dequant, as four groups of two warps; group g owns k-blocks g, g+4, ...: it loads
+//                this CTA's packed words and group scales for its next block from global memory
+//                straight into registers (one block ahead of the stage it is waiting for), then
+//                writes bf16 in the 128-byte-swizzled operand layout the MMA descriptor expects
+//                (generic-proxy stores, fence.proxy.async, one arrival per warp on the leader CTA's
+//                barrier)
 //   warp 1       MMA issuer (leader CTA): waits for both CTAs' A bytes and both CTAs' dequantised
 //                halves, issues four 256 x 256 x 16 MMAs, commits the stage back to both CTAs
 //   warps 2-9    epilogue: TMEM -> registers -> bias -> bf16 -> swizzled staging -> TMA stores
@@ -27,13 +30,14 @@
 // operand: a k-block of 64 reduction rows (d_out) against this CTA's 128 output columns (d_in) is the
 // upper or lower 64 rows of two adjacent packed tiles, each becoming one 64-column MN-major chunk
 // [64 reduction rows][64 columns].  The conversion code is therefore the same for both directions;
-// only the copies' source addresses and the MMA descriptors differ.
+// only the loads' source addresses and the MMA descriptors differ.
 //
 // Conversion: `(word >> 4j) & 0x000F000F | 0x43004300` is the bf16 pair (128 + u, 128 + u') of two
-// adjacent elements (u = q + 8, nibble order chosen at pack time).  EXACT = true reproduces
-// bf16(q * scale) with the f32 product of the scratch-copy path bit for bit; EXACT = false uses two
-// packed bf16 instructions per pair, w = bf16(q * bf16(scale)) (q exact, the scale rounded once,
-// relative 2^-9 — the same rule as the 17..64-token kernel).
+// adjacent elements (u = q + 8, nibble order chosen at pack time).  MODE 1 reproduces
+// bf16(q * scale) with the f32 product of the scratch-copy path bit for bit; MODE 0 uses two packed
+// bf16 instructions per pair, w = bf16(q * bf16(scale)) (q exact, the scale rounded once, relative
+// 2^-9 — the same rule as the 17..64-token kernel); MODE 2 splits the scale into bf16 hi + lo and
+// computes fma(q, s_hi, q * s_lo), which rounds q * scale once except next to a rounding boundary.
 //
 // The LoRA product rides along as extra k-blocks ("K extension") whose operands are plain bf16
 // tiles loaded by TMA into the same stage buffers; the dequant warps pass those blocks through.

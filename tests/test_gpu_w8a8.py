@@ -91,3 +91,37 @@ def test_w8a8_is_refused_for_int_weights_and_f32_activations():
     w8 = lb().fp8_quantize(dev(seeded((64, 64), 5, 0.02)), True)
     with pytest.raises(TypeError, match="bf16 activations"):
         Q.linear_fwd_raw(w8, torch.zeros((8, 64), device="cuda"), None, None, 1.0, fp8_compute=True)
+
+
+def test_w8a8_per_channel_scales_are_applied_to_the_right_channels():
+    """The global band (5e-2 of the output's peak) could hide a wrong scale on a few output channels.
+    Give the channels scales spread over three orders of magnitude and check every output column of Y
+    (scale applied in the epilogue) and every column of dX with a one-hot dY (scale folded into dY on
+    the reduction axis) against the oracle, each column normalised by ITS OWN peak."""
+    from loractl_b200 import quant as Q
+
+    n, k, m = 256, 256, 512
+    rng = np.random.default_rng(3)
+    row_gain = np.exp(rng.uniform(np.log(1e-2), np.log(10.0), size=(m, 1))).astype(np.float32)
+    w = seeded((m, k), 5, 0.02) * row_gain  # per-channel absmax, hence scale, varies 1000-fold
+    x = bf16_round(seeded((n, k), 6))
+    wq = lb().fp8_quantize(dev(w), True)
+    dq = O.fp8_dequant(*O.fp8_quantize(w, True))
+    xd = dev(x, torch.bfloat16)
+    y, _ = Q.linear_fwd_raw(wq, xd, None, None, 1.0, fp8_compute=True)
+    oy, _ = O.lora_linear_fwd(x, dq, None, None, 1.0)
+    yh = host(y)
+    col_peak = np.abs(oy).max(axis=0)
+    col_dev = np.abs(yh - oy).max(axis=0) / col_peak
+    assert col_dev.max() <= 8e-2, (int(col_dev.argmax()), float(col_dev.max()))
+    # backward: dY selects one output channel per token, so row n of dX is s_w[c] * W8[c, :] for c = n % m
+    dy = np.zeros((n, m), np.float32)
+    dy[np.arange(n), (np.arange(n) * 2) % m] = 1.0
+    wq.prepare_fp8_backward()
+    dx, _, _ = Q.linear_bwd_raw(wq, dev(dy, torch.bfloat16), xd, None, None, None, 1.0, fp8_compute=True)
+    lb().check_device_status()
+    odx = O.lora_linear_bwd(dy, x, dq)[0]
+    dxh = host(dx)
+    row_peak = np.abs(odx).max(axis=1)
+    row_dev = np.abs(dxh - odx).max(axis=1) / row_peak
+    assert row_dev.max() <= 8e-2, (int(row_dev.argmax()), float(row_dev.max()))
