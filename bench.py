@@ -914,7 +914,7 @@ def mmdit_step_flops(cfg, lora_rank: int, n_blocks: int, global_batch: int) -> i
 
 
 def measure_train_step(dev, world: int, rank: int, n_blocks: int, batch: int, lora_rank: int, steps: int,
-                       warmup: int, weight_copies: bool = False):
+                       warmup: int, weight_copies: str = "none"):
     """Times `steps` training steps of the double-stream stack on this rank's shard of the global
     batch (max over ranks, CUDA events, barrier + synchronize on both sides).  Returns the result
     dict on every rank; the process group, if any, is the caller's."""
@@ -974,8 +974,10 @@ def measure_train_step(dev, world: int, rank: int, n_blocks: int, batch: int, lo
                    "mlp": cfg.mlp, "lora_rank": lora_rank, "global_batch": global_batch,
                    "samples_per_gpu": b, "tokens_per_sample": tokens, "quant": "int4 block 64",
                    "grad_checkpointing": True, "parallelism": f"dp{world}",
-                   "weight_copies": "resident bf16 copy of every frozen weight (no dequantisation pass)"
-                   if weight_copies else "none (every call dequantises into the workspace)"},
+                   "weight_copies": {"none": "none (every call dequantises into the workspace)",
+                                     "resident": "resident bf16 copy of every frozen weight (no dequantisation pass)",
+                                     "block": "two arenas of one block's bf16 copies, refilled one block ahead "
+                                              "of the sweep on a side stream"}[weight_copies]},
         "model": {"step_flops": step_fl, "tflops": step_fl / (ms / steps * 1e-3) / 1e12,
                   "lora_params": n_params, "grad_bucket_bytes": stack.flat.numel * 4},
         "tokens_per_s": tokens * global_batch * steps / (ms * 1e-3),
@@ -1118,8 +1120,9 @@ def main():
                          "step: LoRA training steps/s of a double-stream MMDiT block stack; "
                          "load: streaming quantize-at-load of one block from a scaled-fp8 checkpoint")
     ap.add_argument("--model", default="mmdit", choices=["mmdit", "gpt2"], help="--regime step: which caller of the path")
-    ap.add_argument("--weight-copies", action="store_true",
-                    help="--regime step: keep a resident bf16 copy of every frozen weight (no dequantisation pass)")
+    ap.add_argument("--weight-copies", nargs="?", const="resident", default="none", choices=["none", "resident", "block"],
+                    help="--regime step: bf16 copies of the frozen weights. resident: of every weight, for the whole "
+                         "run; block: two arenas of one block's copies, refilled one block ahead on a side stream")
     ap.add_argument("--no-extras", action="store_true",
                     help="tensor regime: skip the extra keys (int4_cfg1, stream, model_step) of the default line")
     ap.add_argument("--gpus", type=int, default=1)

@@ -19,7 +19,7 @@ CSRC = PKG / "csrc"
 OBJ = PKG / "lib" / "obj"
 LIB = PKG / "lib" / "libloractl_b200.so"
 HEADER = PKG.parent / "include" / "loractl_b200.h"
-SOURCES = ["lq_api.cu", "lq_quant.cu", "lq_simt.cu", "lq_tc.cu", "lq_w4.cu", "lq_prof.cu", "lq_step.cu", "lq_fused.cu",
+SOURCES = ["lq_api.cu", "lq_quant.cu", "lq_simt.cu", "lq_tc.cu", "lq_w4.cu", "lq_prof.cu", "lq_step.cu", "lq_fused.cu", "lq_bwd_small.cu",
            "lq_block.cu"]
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -31,6 +31,12 @@ class GroupSite(C.Structure):
                 ("Y", C.c_void_p), ("H_out", C.c_void_p)]
 
 
+class MirrorJob(C.Structure):
+    """`lq_mirror_job` of include/loractl_b200.h."""
+    _fields_ = [("A", C.c_void_p), ("B", C.c_void_p), ("d_in", C.c_int64), ("d_out", C.c_int64), ("rank", C.c_int32),
+                ("mirror", C.c_void_p)]
+
+
 class WeightInfo(C.Structure):
     _fields_ = [
         ("d_out", C.c_int64), ("d_in", C.c_int64), ("scheme", C.c_int32), ("group", C.c_int32),
@@ -63,6 +69,7 @@ SIGNATURES = {
     "lq_weight_attach_bf16_copy": (_I, [_P, _P, _P]),
     "lq_lora_mirror_bytes": (_SZ, [_I64, _I64, _I]),
     "lq_lora_mirror_update": (_I, [_P, _P, _I64, _I64, _I, _P, _P]),
+    "lq_lora_mirror_update_batch": (_I, [_P, _I, _P]),
     "lq_linear_grouped_workspace_bytes": (_SZ, [C.POINTER(GroupSite), _I, _I64, _I]),
     "lq_linear_fwd_grouped": (_I, [C.POINTER(GroupSite), _I, _P, _I64, _I, _P, _SZ, _P]),
     "lq_weight_prepare_fp8_backward": (_I, [_P, _P]),

@@ -49,7 +49,7 @@ def checkpointed_step(blocks: Sequence[Callable[[torch.Tensor], torch.Tensor]], 
     loss = head_loss(x_final)
     (loss * loss_scale).backward()
     grad_x = x_final.grad
-    loss_value = float(loss.detach())
+    loss_dev = loss.detach()  # read back after the sweep is enqueued: a host read here would drain the GPU
     # Phase 3 — reverse sweep with per-block replay
     for i in range(len(blocks) - 1, -1, -1):
         x2 = block_inputs[i].detach().requires_grad_(True)
@@ -60,4 +60,4 @@ def checkpointed_step(blocks: Sequence[Callable[[torch.Tensor], torch.Tensor]], 
         if after_block is not None:
             after_block(i)
     grads = [p.grad if p.grad is not None else torch.zeros_like(p) for p in params]
-    return loss_value, grads
+    return float(loss_dev), grads

@@ -392,6 +392,7 @@ size_t lq_linear_workspace_bytes(const lq_weight_t* w, int64_t n_tokens, int ran
     if (dtype == LQ_BF16 && lq_tc_supported(w, n_tokens, rank)) {
         size_t need = lq_tc_workspace_bytes(w, n_tokens, rank);  // backward (and forward for N > 64)
         if (lq_fused_supported(w, n_tokens, rank)) need = std::max(need, lq_fused_workspace_bytes(w, n_tokens, rank));
+        if (lq_small_bwd_supported(w, n_tokens, rank)) need = std::max(need, lq_small_bwd_workspace_bytes(w, n_tokens, rank));
         return align256(need) + 256;
     }
     c.take(sizeof(float) * (size_t)n_tokens * (size_t)(rank > 0 ? rank : 1));  // H
@@ -431,6 +432,24 @@ int lq_lora_mirror_update(const float* A, const float* B, int64_t d_in, int64_t 
         LQ_CUDA(cudaGetDevice(&dev));
         check_sm100(dev);
         lq_tc_mirror_build(A, B, d_in, d_out, rank, mirror, (cudaStream_t)stream);
+    });
+}
+
+int lq_lora_mirror_update_batch(const lq_mirror_job* jobs, int n_jobs, void* stream) {
+    return guarded([&] {
+        LQ_CHECK_ARG(n_jobs >= 0 && (n_jobs == 0 || jobs != nullptr), "jobs is NULL");
+        for (int i = 0; i < n_jobs; ++i) {
+            const lq_mirror_job& q = jobs[i];
+            LQ_CHECK_ARG(q.A && q.B && q.mirror, "NULL pointer in a mirror job");
+            LQ_CHECK_ARG(q.d_in > 0 && q.d_out > 0 && q.rank >= 1 && q.rank <= 256,
+                         "d_in, d_out must be positive and rank in [1, 256]");
+            LQ_CHECK_ARG(((uintptr_t)q.mirror & 255) == 0, "mirror must be 256-byte aligned");
+        }
+        if (n_jobs == 0) return;
+        int dev = 0;
+        LQ_CUDA(cudaGetDevice(&dev));
+        check_sm100(dev);
+        lq_tc_mirror_build_batch(jobs, n_jobs, (cudaStream_t)stream);
     });
 }
 
@@ -487,6 +506,12 @@ int lq_linear_bwd(const lq_weight_t* w, const void* dY, const void* X, const flo
         if (dtype == LQ_BF16_W8A8) {
             lq_w8a8_bwd(w, dY, X, H, n_tokens, A, B, rank, scaling, dX, dA, dB, accumulate, workspace, workspace_bytes,
                         st);
+            return;
+        }
+        if (dtype == LQ_BF16 && lq_tc_supported(w, n_tokens, rank) && lq_small_bwd_supported(w, n_tokens, rank)) {
+            // packed-weight-stream regime of the backward: no bf16 image of W^T is written
+            lq_small_bwd(w, dY, X, H, n_tokens, A, B, rank, scaling, dX, dA, dB, accumulate, workspace, workspace_bytes,
+                         st);
             return;
         }
         if (dtype == LQ_BF16 && lq_tc_supported(w, n_tokens, rank)) {
@@ -581,8 +606,8 @@ int lq_selftest_bounded_wait(unsigned limit_ms, void* stream) {
 int lq_option_set(const char* name, int value) {
     return guarded([&] {
         LQ_CHECK_ARG(name != nullptr, "option name is NULL");
-        if (!lq_w4_option_set(name, value))
-            throw LqError(LQ_ERR_INVALID, std::string("unknown option '") + name + "' (known: w4, w4_exact)");
+        if (!lq_w4_option_set(name, value) && !lq_tc_option_set(name, value))
+            throw LqError(LQ_ERR_INVALID, std::string("unknown option '") + name + "' (known: w4, w4_exact, bwd_mn)");
     });
 }
 

@@ -19,7 +19,9 @@
 //
 // Work items are (output tile, k-split); with splits > 1 the kernel writes f32 partial tiles
 // that a fixed-order second stage reduces (deterministic: no atomics anywhere).
+#include <atomic>
 #include <cstdlib>
+#include <cstring>
 #include <map>
 #include <mutex>
 #include <vector>
@@ -833,6 +835,13 @@ void launch_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand
     LQ_CUDA(cudaGetLastError());
 }
 
+// "bwd_mn": the backward's dX GEMM reads a NON-transposed bf16 scratch as an MN-major operand
+// (LQ_BWD_MN=0 restores the transposed scratch and the K-major operand)
+std::atomic<int> g_bwd_mn{[] {
+    const char* e = getenv("LQ_BWD_MN");
+    return e ? atoi(e) : 1;
+}()};
+
 bool pair_enabled() {
     static const bool on = [] {
         const char* e = getenv("LQ_GEMM_1CTA");
@@ -1412,6 +1421,75 @@ int lq_tc_read_status(int device, cudaStream_t st) {
 
 size_t lq_tc_mirror_bytes(int64_t K, int64_t M, int r) { return r > 0 ? carve_mirror(K, M, r, nullptr).bytes : 0; }
 
+bool lq_tc_option_set(const char* name, int value) {
+    if (std::strcmp(name, "bwd_mn") == 0) { g_bwd_mn = value; return true; }
+    return false;
+}
+
+// The mirrors of many sites in one launch (a trainer refreshes all of them after an optimizer step):
+// blockIdx.y is the site, the launch parameter carries up to kMirrorBatch sites.
+constexpr int kMirrorBatch = 24;
+struct MirrorJob {
+    const float *A, *B;
+    long long K, M;
+    int r, EXT;
+    LoraMirror m;
+};
+struct MirrorBatch {
+    MirrorJob job[kMirrorBatch];
+};
+__global__ void __launch_bounds__(256) lora_mirror_batch_kernel(const __grid_constant__ MirrorBatch mb) {
+    const MirrorJob& j = mb.job[blockIdx.y];
+    const float* __restrict__ A = j.A;
+    const float* __restrict__ B = j.B;
+    const long long K = j.K, M = j.M;
+    const int r = j.r, EXT = j.EXT;
+    const long long n0 = (long long)r * K, n1 = M * EXT, n2 = (long long)r * M, n3 = K * EXT;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n0 + n1 + n2 + n3;
+         i += (long long)gridDim.x * blockDim.x) {
+        if (i < n0) {
+            const long long jj = i / K, k = i - jj * K;
+            j.m.At[i] = __float2bfloat16(A[k * r + jj]);
+        } else if (i < n0 + n1) {
+            const long long t = i - n0, mm = t / EXT;
+            const int c = (int)(t - mm * EXT);
+            j.m.Bt[t] = __float2bfloat16(c < r ? B[(long long)c * M + mm] : 0.f);
+        } else if (i < n0 + n1 + n2) {
+            const long long t = i - n0 - n1;
+            j.m.Bb[t] = __float2bfloat16(B[t]);
+        } else {
+            const long long t = i - n0 - n1 - n2, k = t / EXT;
+            const int c = (int)(t - k * EXT);
+            j.m.Ap[t] = __float2bfloat16(c < r ? A[k * r + c] : 0.f);
+        }
+    }
+}
+
+void lq_tc_mirror_build_batch(const lq_mirror_job* jobs, int n, cudaStream_t st) {
+    for (int base = 0; base < n; base += kMirrorBatch) {
+        const int cnt = std::min(kMirrorBatch, n - base);
+        MirrorBatch mb;
+        long long most = 0;
+        for (int i = 0; i < cnt; ++i) {
+            const lq_mirror_job& q = jobs[base + i];
+            MirrorJob& j = mb.job[i];
+            j.A = q.A;
+            j.B = q.B;
+            j.K = q.d_in;
+            j.M = q.d_out;
+            j.r = q.rank;
+            j.EXT = ext_width(q.rank);
+            j.m = carve_mirror(q.d_in, q.d_out, q.rank, q.mirror);
+            most = std::max(most, (long long)j.r * j.K + j.M * j.EXT + (long long)j.r * j.M + j.K * j.EXT);
+        }
+        for (int i = cnt; i < kMirrorBatch; ++i) mb.job[i] = mb.job[0];
+        LqProf prof(LQ_K_PREP, st);
+        dim3 grid((unsigned)std::min<long long>((most + 255) / 256, 64), (unsigned)cnt);
+        lora_mirror_batch_kernel<<<grid, 256, 0, st>>>(mb);
+        LQ_CUDA(cudaGetLastError());
+    }
+}
+
 void lq_tc_mirror_build(const float* A, const float* B, int64_t K, int64_t M, int r, void* mirror, cudaStream_t st) {
     LoraMirror m = carve_mirror(K, M, r, mirror);
     const int EXT = ext_width(r);
@@ -1488,12 +1566,18 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
     const bool w4 = dX && !w->bf16_copy && lq_w4_supported(w, N, 1);
     // a resident bf16 copy [M, K] is read as an MN-major B operand (reduction over its rows) by the
     // CTA-pair kernel: no transposed scratch is written
-    const bool cached = dX && w->bf16_copy && pair_enabled() && N >= 256 && K > 192 && ctx.sm_count >= 2;
-    Operand bmn{w->bf16_copy, true, K};
+    const bool mn_ok = dX && pair_enabled() && N >= 256 && K > 192 && ctx.sm_count >= 2;
+    const bool cached = mn_ok && w->bf16_copy;
+    // without a resident copy the same operand form serves the per-call scratch: the weight is
+    // dequantised in its own [M, K] orientation (the cheaper pass: full output lines per warp, no
+    // staging) and the dX GEMM reads the scratch MN-major
+    const bool mn_scratch = mn_ok && !cached && !w4 && g_bwd_mn.load() != 0 && K % 8 == 0;
+    Operand bmn{cached ? (const void*)w->bf16_copy : (const void*)t.wscr, true, K};
     if (r == 0) {
         if (dX && w4) {
             lq_w4_gemm(w, 1, dY, M, nullptr, 0, nullptr, 0, 0, dX, K, N, nullptr, st);
-        } else if (dX && cached) {
+        } else if (dX && (cached || mn_scratch)) {
+            if (mn_scratch) lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, st);
             launch_gemm_pair<256, false, true>(a0, bmn, M, nullptr, nullptr, 0, (__nv_bfloat16*)dX, K, N, K, nullptr, st);
         } else if (dX) {
             lq_launch_dequant(w, t.wscr, LQ_BF16, M, 1, st);  // W^T [K, M]
@@ -1511,7 +1595,8 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
     fj.fork();
     // side: what the dX GEMM needs besides dH: W^T [K, M] and A [K, EXT] in bf16
     if (dX) {
-        if (!w4 && !cached) lq_launch_dequant(w, t.wscr, LQ_BF16, M, 1, fj.side());
+        if (mn_scratch) lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, fj.side());       // W [M, K]
+        else if (!w4 && !cached) lq_launch_dequant(w, t.wscr, LQ_BF16, M, 1, fj.side());  // W^T [K, M]
         if (!mirror) cast_pad(A, r, 1, t.pext, EXT, K, r, EXT, 1.f, fj.side());
     }
     fj.record(0);  // the caller's stream waits for this point just before the dX GEMM
@@ -1538,7 +1623,7 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
         fj.wait(0);
         if (w4) {
             lq_w4_gemm(w, 1, dY, M, t.ext_a, EXT, t.pext, EXT, EXT, dX, K, N, nullptr, st);
-        } else if (cached) {
+        } else if (cached || mn_scratch) {
             Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
             launch_gemm_pair<256, false, true>(a0, bmn, M, &a1, &b1, EXT, (__nv_bfloat16*)dX, K, N, K, nullptr, st);
         } else {

@@ -19,6 +19,7 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
                size_t ws_bytes, cudaStream_t st, const void* mirror);
 size_t lq_tc_mirror_bytes(int64_t K, int64_t M, int r);
 void lq_tc_mirror_build(const float* A, const float* B, int64_t K, int64_t M, int r, void* mirror, cudaStream_t st);
+void lq_tc_mirror_build_batch(const lq_mirror_job* jobs, int n, cudaStream_t st);
 
 // Plain bf16 GEMM entry used by tests and probes: C[Mg,Ng] = A . B^T with either operand
 // K-major ([rows, Kg], Kg contiguous) or MN-major ([Kg, rows], rows contiguous).
@@ -57,6 +58,14 @@ size_t lq_fused_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank);
 void lq_fused_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, const float* B, int r, float s,
                   void* Y, float* H_out, void* ws, size_t ws_bytes, cudaStream_t st);
 
+// Small-batch backward (int4 block-64 weights at N <= 16 tokens): dX over the packed stream with the
+// weights converted in registers, dH / dA / dB in the same two launches (lq_bwd_small.cu).
+bool lq_small_bwd_supported(const lq_weight* w, int64_t n_tokens, int rank);
+size_t lq_small_bwd_workspace_bytes(const lq_weight* w, int64_t n_tokens, int rank);
+void lq_small_bwd(const lq_weight* w, const void* dY, const void* X, const float* H, int64_t N, const float* A,
+                  const float* B, int r, float s, void* dX, float* dA, float* dB, int accumulate, void* ws,
+                  size_t ws_bytes, cudaStream_t st);
+
 // A group of sites that share X, as one launch of the <= 16-token stream kernel plus one finalize.
 bool lq_fused_group_supported(const lq_group_site* sites, int n_sites, int64_t n_tokens);
 size_t lq_fused_group_workspace_bytes(const lq_group_site* sites, int n_sites, int64_t n_tokens);
@@ -79,6 +88,7 @@ void lq_w8a8_bwd(const lq_weight* w, const void* dY, const void* X, const float*
 // A0[Mg, d_out] . W.  (a1, b1): optional bf16 K extension [Mg, K1] / [Ng, K1] (the LoRA product).
 bool lq_w4_supported(const lq_weight* w, int64_t Mg, int transposed);
 bool lq_w4_option_set(const char* name, int value);  // "w4", "w4_exact"; false: unknown name
+bool lq_tc_option_set(const char* name, int value);  // "bwd_mn"; false: unknown name
 void lq_w4_gemm(const lq_weight* w, int transposed, const void* A0, int64_t lda, const void* a1, int64_t lda1,
                 const void* b1, int64_t ldb1, int64_t K1, void* Cout, int64_t ldc, int64_t Mg, const float* bias,
                 cudaStream_t st);

@@ -31,6 +31,7 @@ from .adapters import LoraAdapters, LoraConfig, LoraSite, TargetSpec, build_adap
 from .block_ckpt import checkpointed_step
 from .block_ops import gated_residual, modulated_layer_norm
 from .linear import BaseLinear, QuantLinear, site, site_group
+from .prefetch import BlockWeightPrefetcher
 from .optim import AdamW, DynamicLossScale, FlatAdapters, nonfinite_flag
 from .quant import quantize_linear_weight
 
@@ -112,10 +113,18 @@ class BlockStack(nn.Module):
     """`n_blocks` double-stream blocks with one LoRA adapter set over every linear."""
 
     def __init__(self, n_blocks: int, cfg: BlockConfig, rank: int, alpha: float, device, seed: int = 5,
-                 dtype: torch.dtype = torch.bfloat16, weight_copies: bool = False):
-        """`weight_copies`: keep a resident bf16 copy of every frozen weight (2 bytes per element beside
-        the packed 0.5), so that no call dequantises — the memory-for-time trade a 180 GB GPU allows."""
+                 dtype: torch.dtype = torch.bfloat16, weight_copies="none"):
+        """`weight_copies`: "none" — every call dequantises into its workspace; "resident" (or True) —
+        keep a bf16 copy of every frozen weight (2 bytes per element beside the packed 0.5), so that no
+        call dequantises: the memory-for-time trade a 180 GB GPU allows; "block" — two arenas of one
+        block's copies each, refilled one block ahead of the sweep on a side stream
+        (`prefetch.BlockWeightPrefetcher`).  The one-token modulation sites never read a copy (their
+        forward streams the packed bytes) and get none."""
         super().__init__()
+        weight_copies = {True: "resident", False: "none", None: "none"}.get(weight_copies, weight_copies)
+        if weight_copies not in ("none", "resident", "block"):
+            raise ValueError(f"weight_copies must be none, resident or block, got {weight_copies!r}")
+        self.weight_copies = weight_copies
         gen = torch.Generator(device=device).manual_seed(seed)
         self.cfg, self.dtype = cfg, dtype
         self.blocks = nn.ModuleList(DoubleStreamBlock(i, cfg, gen, device) for i in range(n_blocks))
@@ -129,14 +138,37 @@ class BlockStack(nn.Module):
                 d.lora_b.copy_(torch.randn(d.lora_b.shape, generator=g2, device=device) * 0.01)
         for blk in self.blocks:
             blk.adapters = self.adapters
-            if weight_copies:
-                for base in blk.bases.values():
-                    base.inner.weight.attach_bf16_copy()
+            if weight_copies == "resident":
+                for w in self._copy_weights(blk):
+                    w.attach_bf16_copy()
+        self.prefetcher = (BlockWeightPrefetcher([self._copy_weights(blk) for blk in self.blocks], device)
+                           if weight_copies == "block" else None)
         self.flat = FlatAdapters(self.adapters, device)
         # slice of the flat buffers that holds block i's adapters (registration order = block order)
         per_block = 2 * len(DoubleStreamBlock.STREAMS) * len(DoubleStreamBlock.LINEARS)
         offs = self.flat.offsets + [self.flat.numel]
         self.block_slices = [(offs[i * per_block], offs[(i + 1) * per_block]) for i in range(n_blocks)]
+
+    @staticmethod
+    def _copy_weights(blk: DoubleStreamBlock):
+        return [base.inner.weight for key, base in blk.bases.items() if not key.endswith("_mod")]
+
+    def block_callables(self):
+        """The blocks as `x -> x` callables for `checkpointed_step` / `forward`.  In "block" mode each
+        one first makes its own weight copies current and starts the refill for the block the sweep
+        visits next: i + 1 on the graph-free forward sweep, i - 1 while replaying for the backward."""
+        if self.prefetcher is None:
+            return list(self.blocks)
+        pf = self.prefetcher
+
+        def wrap(i, blk):
+            def run(x):
+                pf.acquire(i)
+                pf.prefetch(i - 1 if torch.is_grad_enabled() else i + 1)
+                return blk(x)
+            return run
+
+        return [wrap(i, blk) for i, blk in enumerate(self.blocks)]
 
     def lora_parameters(self):
         return [p for d in self.adapters.deltas for p in (d.lora_a, d.lora_b)]
@@ -146,7 +178,7 @@ class BlockStack(nn.Module):
             blk.cond = cond
 
     def forward(self, state: torch.Tensor) -> torch.Tensor:
-        for blk in self.blocks:
+        for blk in self.block_callables():
             state = blk(state)
         return state
 
@@ -186,7 +218,7 @@ class Trainer:
                     flat.gather_autograd_grads(stack.block_slices[i])
                     reducer.reduce_slice(*stack.block_slices[i])
 
-            loss, _ = checkpointed_step(list(stack.blocks), state, head, params, self.scaler.loss_scale,
+            loss, _ = checkpointed_step(stack.block_callables(), state, head, params, self.scaler.loss_scale,
                                         keep_existing_grads=True, after_block=after_block)
             flat.gather_autograd_grads()
         else:
@@ -202,6 +234,7 @@ class Trainer:
         # the optimizer reads the flag on the device and skips itself; the host reads it only to
         # advance the loss-scale state (where the reference reads its |g| sum back)
         self.optim.step(self.lr, grad_scale=scale / self.scaler.loss_scale, skip_flag=flat.flag)
+        flat.refresh_mirrors()  # the factors changed: all bf16 operand mirrors in one batched launch
         finite, _ = dp.consensus_step(self.scaler, flat.flag)
         if not finite:
             self.optim.steps -= 1  # a skipped update does not advance the bias-correction clock

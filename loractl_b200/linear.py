@@ -86,14 +86,24 @@ class BaseLinear(nn.Module):
         return self.inner(x)
 
 
+def _grads_live_in(bucket, a: torch.Tensor, b: torch.Tensor) -> bool:
+    """True when `a.grad` / `b.grad` currently ARE the bucket views: only then may the backward add
+    into the bucket itself (a caller that reset `.grad` expects autograd to fill it)."""
+    return (bucket is not None and a.grad is not None and b.grad is not None
+            and a.grad.data_ptr() == bucket[0].data_ptr() and b.grad.data_ptr() == bucket[1].data_ptr())
+
+
 class _LoraLinearFn(torch.autograd.Function):
     """One LoRA'd quantized site.  Saves x and H = x.A for the backward; the frozen weight is
     state (quant.rs:217-219), never a graph parent."""
 
     @staticmethod
-    def forward(ctx, x2, a, b, wq, scaling, mirror):
+    def forward(ctx, x2, a, b, wq, scaling, mirror, bucket=None):
+        """`bucket` = (dA view, dB view) of a flat gradient buffer: the backward adds into them in place
+        (what autograd's accumulation into `.grad` would do with two more kernels) and returns no
+        gradient for `a`, `b`."""
         y, h = Q.linear_fwd_raw(wq, x2, a, b, scaling, mirror=mirror)
-        ctx.wq, ctx.scaling, ctx.mirror = wq, scaling, mirror
+        ctx.wq, ctx.scaling, ctx.mirror, ctx.bucket = wq, scaling, mirror, bucket
         ctx.save_for_backward(x2, h, a, b)
         return y
 
@@ -101,9 +111,14 @@ class _LoraLinearFn(torch.autograd.Function):
     def backward(ctx, dy):
         x2, h, a, b = ctx.saved_tensors
         need_dx, need_da, need_db = ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.needs_input_grad[2]
+        if _grads_live_in(ctx.bucket, a, b):
+            dx, _, _ = Q.linear_bwd_raw(ctx.wq, dy.contiguous(), x2, h, a, b, ctx.scaling, need_dx=need_dx,
+                                        need_da=need_da, need_db=need_db, da_out=ctx.bucket[0], db_out=ctx.bucket[1],
+                                        accumulate=True, mirror=ctx.mirror)
+            return dx, None, None, None, None, None, None
         dx, da, db = Q.linear_bwd_raw(ctx.wq, dy.contiguous(), x2, h, a, b, ctx.scaling,
                                       need_dx=need_dx, need_da=need_da, need_db=need_db, mirror=ctx.mirror)
-        return dx, da, db, None, None, None
+        return dx, da, db, None, None, None, None
 
 
 def _fused(wq: Q.QuantWeight, x: torch.Tensor, delta: Optional[LoraDelta]) -> torch.Tensor:
@@ -122,7 +137,7 @@ def _fused(wq: Q.QuantWeight, x: torch.Tensor, delta: Optional[LoraDelta]) -> to
                 "(the fused kernel has no dropout; the reference also forbids it under recompute)")
         # bf16 activations take the tensor-core path, which wants the factors as bf16 operands
         mirror = delta.operand_mirror() if x2.dtype == torch.bfloat16 else None
-        y = _LoraLinearFn.apply(x2, delta.lora_a, delta.lora_b, wq, delta.scaling, mirror)
+        y = _LoraLinearFn.apply(x2, delta.lora_a, delta.lora_b, wq, delta.scaling, mirror, delta.bucket_grads)
     return y.reshape(*lead, wq.d_out)
 
 
@@ -133,7 +148,7 @@ class _GroupedLoraLinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x2, meta, *factors):
         sites = []
-        for i, (wq, scaling, has_delta, _) in enumerate(meta):
+        for i, (wq, scaling, has_delta, _, _) in enumerate(meta):
             a, b = (factors[2 * i], factors[2 * i + 1]) if has_delta else (None, None)
             sites.append((wq, a, b, scaling))
         outs = Q.linear_fwd_grouped_raw(sites, x2)
@@ -148,16 +163,19 @@ class _GroupedLoraLinearFn(torch.autograd.Function):
         hs = ctx.saved_tensors[1:1 + n]
         factors = ctx.saved_tensors[1 + n:]
         dx_total, grads = None, []
-        for i, (wq, scaling, has_delta, mirror) in enumerate(ctx.meta):
+        for i, (wq, scaling, has_delta, mirror, bucket) in enumerate(ctx.meta):
             a, b = (factors[2 * i], factors[2 * i + 1]) if has_delta else (None, None)
             h = hs[i] if has_delta else None
             need_dx = ctx.needs_input_grad[0]
+            direct = has_delta and _grads_live_in(bucket, a, b)
             dx, da, db = Q.linear_bwd_raw(wq, dys[i].contiguous(), x2, h, a, b, scaling, need_dx=need_dx,
                                           need_da=has_delta and ctx.needs_input_grad[2 + 2 * i],
-                                          need_db=has_delta and ctx.needs_input_grad[3 + 2 * i], mirror=mirror)
+                                          need_db=has_delta and ctx.needs_input_grad[3 + 2 * i], mirror=mirror,
+                                          da_out=bucket[0] if direct else None, db_out=bucket[1] if direct else None,
+                                          accumulate=direct)
             if dx is not None:
                 dx_total = dx if dx_total is None else dx_total + dx
-            grads += [da, db]
+            grads += [None, None] if direct else [da, db]
         return (dx_total, None, *grads)
 
 
@@ -179,7 +197,8 @@ def site_group(adapters: Optional[LoraAdapters], sites, x: torch.Tensor):
     meta, factors = [], []
     for (_, base), d in zip(sites, deltas):
         mirror = d.operand_mirror() if (d is not None and x2.dtype == torch.bfloat16) else None
-        meta.append((base.inner.weight, d.scaling if d is not None else 1.0, d is not None, mirror))
+        meta.append((base.inner.weight, d.scaling if d is not None else 1.0, d is not None, mirror,
+                     d.bucket_grads if d is not None else None))
         if d is not None:
             factors += [d.lora_a, d.lora_b]
         else:  # placeholders keep the argument positions regular

@@ -41,6 +41,13 @@ class LoraDelta(nn.Module):
         self._mirror: Optional[torch.Tensor] = None
         self._mirror_key = None
         self.param_epoch = [0]
+        # (dA view, dB view) of a flat gradient bucket, set by `FlatAdapters`: the fused backward then adds
+        # straight into them instead of returning fresh tensors for autograd to accumulate
+        self.bucket_grads = None
+
+    def _mirror_state(self):
+        a, b = self.lora_a, self.lora_b
+        return (a._version, b._version, a.data_ptr(), b.data_ptr(), self.param_epoch[0])
 
     def operand_mirror(self) -> Optional[torch.Tensor]:
         """The factors as bf16 GEMM operands (`lq_lora_mirror_update`), refreshed with one launch
@@ -48,7 +55,7 @@ class LoraDelta(nn.Module):
         a, b = self.lora_a, self.lora_b
         if not a.is_cuda:
             return None
-        key = (a._version, b._version, a.data_ptr(), b.data_ptr(), self.param_epoch[0])
+        key = self._mirror_state()
         if self._mirror is None or self._mirror_key != key:
             from . import quant as Q
 

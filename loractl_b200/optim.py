@@ -77,8 +77,30 @@ class FlatAdapters:
             p.grad = self.grads[o:o + p.numel()].view(p.shape)
         self._params = params
         self.param_epoch = [0]  # shared with every delta: bumped when a kernel rewrites `params`
-        for d in adapters.deltas:
+        for i, d in enumerate(adapters.deltas):
             d.param_epoch = self.param_epoch
+            d.bucket_grads = (params[2 * i].grad, params[2 * i + 1].grad)
+
+    def refresh_mirrors(self) -> None:
+        """Rebuilds the bf16 operand mirror of every adapter whose factors changed since it was built,
+        with one launch per 24 adapters (after `AdamW.step`, instead of one launch per site at its
+        first use in the next forward)."""
+        from . import quant as Q
+
+        if not self.params.is_cuda:
+            return
+        jobs, stale = [], []
+        for d in self.adapters.deltas:
+            key = d._mirror_state()
+            if d._mirror is not None and d._mirror_key == key:
+                continue
+            if d._mirror is None:
+                d._mirror = Q.lora_mirror_alloc(d.lora_a, d.lora_b)
+            jobs.append((d.lora_a.detach(), d.lora_b.detach(), d._mirror))
+            stale.append((d, key))
+        Q.lora_mirror_batch(jobs)
+        for d, key in stale:
+            d._mirror_key = key
 
     def grad_views(self, index: int):
         """(dA view, dB view) of delta `index` — pass them to `lq_linear_bwd` as outputs."""

@@ -272,6 +272,32 @@ def lora_mirror(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = 
     return out
 
 
+def lora_mirror_alloc(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """An uninitialised, 256-byte aligned mirror buffer for factors of these shapes."""
+    d_in, r = a.shape
+    need = int(L.lib().lq_lora_mirror_bytes(d_in, b.shape[1], r))
+    raw = torch.empty(need + 256, dtype=torch.uint8, device=a.device)
+    off = (-raw.data_ptr()) % 256
+    return raw[off:off + need]
+
+
+def lora_mirror_batch(jobs) -> None:
+    """Refreshes many mirrors with one launch per 24 sites (`lq_lora_mirror_update_batch`).  `jobs` is a
+    sequence of (a [d_in, r], b [r, d_out], mirror buffer) on one device."""
+    jobs = list(jobs)
+    if not jobs:
+        return
+    import ctypes as C
+
+    arr = (L.MirrorJob * len(jobs))()
+    for i, (a, b, m) in enumerate(jobs):
+        _require_cuda(a, "lora_a")
+        arr[i] = L.MirrorJob(a.data_ptr(), b.data_ptr(), a.shape[0], b.shape[1], a.shape[1], m.data_ptr())
+    dev = jobs[0][0].device
+    with torch.cuda.device(dev):
+        L.check(L.lib().lq_lora_mirror_update_batch(C.cast(arr, C.c_void_p), len(jobs), _stream_ptr(dev)))
+
+
 def linear_fwd_raw(wq: QuantWeight, x2: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor],
                    scaling: float, want_h: bool = True, fp8_compute: bool = False,
                    mirror: Optional[torch.Tensor] = None):

@@ -84,3 +84,25 @@ def test_mirror_arguments_are_validated():
     off = (-buf.data_ptr()) % 256 + 16  # misaligned on purpose
     rc = L.lib().lq_lora_mirror_update(a.data_ptr(), b.data_ptr(), 256, 512, 16, buf.data_ptr() + off, None)
     assert rc == L.LQ_ERR_INVALID
+
+
+def test_batched_mirror_update_equals_per_site_updates():
+    """`lq_lora_mirror_update_batch` over many sites (more than one launch's worth, mixed shapes and
+    ranks) writes exactly the bytes of one `lq_lora_mirror_update` per site."""
+    from loractl_b200 import quant as Q
+
+    shapes = [(256 + 64 * (i % 3), 128 + 128 * (i % 4), (4, 16, 32, 80)[i % 4]) for i in range(29)]
+    jobs, singles = [], []
+    for i, (k, m, r) in enumerate(shapes):
+        a, b = dev(seeded((k, r), 50 + i, 0.1)), dev(seeded((r, m), 90 + i, 0.1))
+        ref = Q.lora_mirror_alloc(a, b)
+        ref.fill_(0xFF)  # the alignment gaps between the four arrays are written by neither route
+        singles.append(Q.lora_mirror(a, b, ref))
+        buf = Q.lora_mirror_alloc(a, b)
+        buf.fill_(0xFF)
+        jobs.append((a, b, buf))
+    Q.lora_mirror_batch(jobs)
+    torch.cuda.synchronize()
+    for (a, b, buf), ref in zip(jobs, singles):
+        assert torch.equal(buf, ref)
+    Q.lora_mirror_batch([])  # an empty batch is a no-op
