@@ -592,7 +592,7 @@ def run_ours(args):
                      "peak": sus_peak, "frac": sus_tf / sus_peak if sus_peak else None,
                      "sm_mhz_median": sampler.median_sm_mhz(t_sus0, t_sus1) if sampler else None}
         # config 5: the 24-block stack, global batch 8 sharded over the ranks, rank 32, recompute on
-        extras["model_step"] = measure_train_step(dev, world, rank, 24, 8, 32, steps=3, warmup=2)
+        extras["model_step"] = measure_train_step(dev, world, rank, 24, 8, 32, steps=3, warmup=2, weight_copies="block")
     clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
 
     flops = step_flops(n, k, m, r)
@@ -914,7 +914,7 @@ def mmdit_step_flops(cfg, lora_rank: int, n_blocks: int, global_batch: int) -> i
 
 
 def measure_train_step(dev, world: int, rank: int, n_blocks: int, batch: int, lora_rank: int, steps: int,
-                       warmup: int, weight_copies: str = "none"):
+                       warmup: int, weight_copies: str = "none", graphs: bool = True):
     """Times `steps` training steps of the double-stream stack on this rank's shard of the global
     batch (max over ranks, CUDA events, barrier + synchronize on both sides).  Returns the result
     dict on every rank; the process group, if any, is the caller's."""
@@ -930,7 +930,7 @@ def measure_train_step(dev, world: int, rank: int, n_blocks: int, batch: int, lo
     lo, hi = lb.dp.shard_range(global_batch, rank, world)
     b = hi - lo
     stack = BlockStack(n_blocks, cfg, lora_rank, float(lora_rank), dev, seed=5, weight_copies=weight_copies)
-    trainer = Trainer(stack, lr=1e-4)
+    trainer = Trainer(stack, lr=1e-4, graphs=graphs)
     g = torch.Generator(device=dev).manual_seed(100 + rank)  # per-rank data, identical weights
     h = cfg.hidden
     x0 = torch.randn((b, cfg.img_tokens, h), generator=g, device=dev, dtype=torch.bfloat16)
@@ -974,6 +974,8 @@ def measure_train_step(dev, world: int, rank: int, n_blocks: int, batch: int, lo
                    "mlp": cfg.mlp, "lora_rank": lora_rank, "global_batch": global_batch,
                    "samples_per_gpu": b, "tokens_per_sample": tokens, "quant": "int4 block 64",
                    "grad_checkpointing": True, "parallelism": f"dp{world}",
+                   "cuda_graphs": "one per block forward, one head, one per block replay + backward" if graphs
+                   else "none (eager launches)",
                    "weight_copies": {"none": "none (every call dequantises into the workspace)",
                                      "resident": "resident bf16 copy of every frozen weight (no dequantisation pass)",
                                      "block": "two arenas of one block's bf16 copies, refilled one block ahead "
@@ -1010,7 +1012,7 @@ def run_train_step(args):
         line = measure_gpt2_step(dev, world, rank, args.steps, args.warmup)
     else:
         line = measure_train_step(dev, world, rank, args.blocks, args.batch, args.rank, args.steps, args.warmup,
-                                  weight_copies=args.weight_copies)
+                                  weight_copies=args.weight_copies, graphs=not args.no_graph)
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -1120,7 +1122,7 @@ def main():
                          "step: LoRA training steps/s of a double-stream MMDiT block stack; "
                          "load: streaming quantize-at-load of one block from a scaled-fp8 checkpoint")
     ap.add_argument("--model", default="mmdit", choices=["mmdit", "gpt2"], help="--regime step: which caller of the path")
-    ap.add_argument("--weight-copies", nargs="?", const="resident", default="none", choices=["none", "resident", "block"],
+    ap.add_argument("--weight-copies", nargs="?", const="resident", default="block", choices=["none", "resident", "block"],
                     help="--regime step: bf16 copies of the frozen weights. resident: of every weight, for the whole "
                          "run; block: two arenas of one block's copies, refilled one block ahead on a side stream")
     ap.add_argument("--no-extras", action="store_true",

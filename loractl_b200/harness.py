@@ -183,15 +183,149 @@ class BlockStack(nn.Module):
         return state
 
 
+class GraphedSweep:
+    """The block-checkpointed forward / head / reverse sweep of one step as CUDA graphs: one graph per
+    block for the graph-free forward, one for the head (loss and its gradient), one per block for
+    replay + backward — 2 L + 1 launches per step instead of some four hundred per block, so a small
+    per-GPU batch is no longer bound by the host.  All graphs share one memory pool and are replayed
+    in the order they were captured.  Static inputs: the trunk input, the conditioning vector, the
+    regression target and the loss scale; each block's forward output is the next block's static
+    input and stays alive as that block's checkpoint; adapter gradients go straight into the flat
+    bucket (fixed addresses); the bf16 operand mirrors keep their buffers and are refreshed outside
+    the graphs.  Captured for one batch shape; a different shape captures a new set.
+
+    With `weight_copies="block"` the refill of the NEXT block's bf16 weight copies is a parallel branch
+    inside the current block's graph (the dequantisation kernels of `attach_bf16_copy`, captured on a
+    forked stream and joined at the end): forward graph i fills block i + 1, replay graph i fills block
+    i - 1, each into the arena the sweep left two blocks ago.  Blocks 0 and 1 are filled once, eagerly:
+    a sweep ends with exactly those two in place."""
+
+    def __init__(self, stack: "BlockStack", state_shape, cond_shape, target_shape):
+        dev = stack.flat.params.device
+        self.stack = stack
+        self.state = torch.zeros(state_shape, dtype=stack.dtype, device=dev)
+        self.cond = torch.zeros(cond_shape, dtype=torch.bfloat16, device=dev)
+        self.target = torch.zeros(target_shape, dtype=torch.float32, device=dev)
+        self.loss_scale = torch.ones((), dtype=torch.float32, device=dev)
+        self.stream = torch.cuda.Stream(device=dev)
+        self.fwd, self.bwd, self.head = [], [], None
+        self.loss = None
+
+    def _head(self, s: torch.Tensor) -> torch.Tensor:
+        li = self.stack.cfg.img_tokens
+        return ((s[:, :li].float() - self.target) ** 2).mean()
+
+    def capture(self) -> None:
+        stack = self.stack
+        blocks = list(stack.blocks)
+        stack.set_cond(self.cond)
+        stack.flat.refresh_mirrors()
+        pf, n_blocks = stack.prefetcher, len(blocks)
+        if pf is not None:  # the two blocks every sweep starts from, for real
+            pf.release_all()
+            pf.fill(0, torch.cuda.current_stream())
+            pf.fill(1, torch.cuda.current_stream())
+        # one eager pass on the capture stream: library plans, workspaces and side streams come into being here
+        self.stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.stream):
+            x = self.state
+            with torch.no_grad():
+                for blk in blocks[:1] + blocks[-1:]:
+                    x = blk(x)
+            x2 = self.state.detach().requires_grad_(True)
+            out = blocks[0](x2)
+            (self._head(out) * self.loss_scale).backward()
+        torch.cuda.current_stream().wait_stream(self.stream)
+        torch.cuda.synchronize()
+        stack.flat.zero_grad()
+        pool = torch.cuda.graph_pool_handle()
+
+        forked = [False]
+
+        def refill(j: int) -> None:
+            """Inside a capture: block j's copies rebuilt on the prefetch stream, beside the block's own work."""
+            if pf is None or j < 0 or j >= n_blocks:
+                return
+            pf.stream.wait_stream(torch.cuda.current_stream())
+            pf.fill(j, pf.stream)
+            forked[0] = True
+
+        def join() -> None:
+            # only a stream that joined this capture may be waited for inside it
+            if forked[0]:
+                torch.cuda.current_stream().wait_stream(pf.stream)
+                forked[0] = False
+
+        inputs = [self.state]
+        for i, blk in enumerate(blocks):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=pool, stream=self.stream, capture_error_mode="thread_local"):
+                if 1 <= i <= n_blocks - 2:
+                    refill(i + 1)
+                with torch.no_grad():
+                    out = blk(inputs[-1])
+                join()
+            self.fwd.append(g)
+            inputs.append(out)
+        self.head = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.head, pool=pool, stream=self.stream, capture_error_mode="thread_local"):
+            x_final = inputs[-1].detach().requires_grad_(True)
+            loss = self._head(x_final)
+            (loss * self.loss_scale).backward()
+            grad = x_final.grad
+            self.loss = loss.detach()
+        self.bwd = [None] * len(blocks)
+        from . import quant as Q
+
+        # what the graphs' kernels point at must outlive them: checkpoints, gradients, call workspaces
+        self._keep = [inputs, grad, list(Q._workspaces.values())]
+        for i in range(len(blocks) - 1, -1, -1):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=pool, stream=self.stream, capture_error_mode="thread_local"):
+                if 1 <= i <= n_blocks - 2:
+                    refill(i - 1)
+                x2 = inputs[i].detach().requires_grad_(True)
+                out = blocks[i](x2)
+                out.backward(gradient=grad)
+                grad = x2.grad
+                join()
+            self.bwd[i] = g
+            self._keep.append(grad)
+        if pf is not None:
+            # the graphs carry the arena addresses; the handles themselves go back to per-call
+            # dequantisation so that eager calls outside the graphs stay correct
+            pf.release_all()
+        stack.flat.zero_grad()  # the captures themselves ran nothing, but keep the bucket's state obvious
+
+    def run(self, state: torch.Tensor, cond: torch.Tensor, target: torch.Tensor, loss_scale: float, after_block) -> torch.Tensor:
+        self.state.copy_(state)
+        self.cond.copy_(cond)
+        self.target.copy_(target)
+        self.loss_scale.fill_(loss_scale)
+        for g in self.fwd:
+            g.replay()
+        self.head.replay()
+        for i in range(len(self.bwd) - 1, -1, -1):
+            self.bwd[i].replay()
+            after_block(i)
+        return self.loss
+
+
 class Trainer:
     """One rank of the data-parallel LoRA trainer over a `BlockStack`."""
 
     def __init__(self, stack: BlockStack, lr: float = 1e-4, weight_decay: float = 1e-4, group=None,
-                 grad_checkpointing: bool = True):
+                 grad_checkpointing: bool = True, graphs: bool = False):
+        """`graphs`: run the checkpointed sweep as CUDA graphs (`GraphedSweep`), captured at the first
+        step of each batch shape."""
         self.stack, self.lr, self.group = stack, lr, group
         self.optim = AdamW(stack.flat, weight_decay=weight_decay)
         self.scaler = DynamicLossScale(initial=1.0)  # bf16/f32 gradients do not need the f16 head-room
         self.grad_checkpointing = grad_checkpointing
+        if graphs and not grad_checkpointing:
+            raise ValueError("graphs=True captures the block-checkpointed sweep: it needs grad_checkpointing")
+        self.graphs = graphs
+        self._sweeps = {}
         self.steps_done = 0
 
     def step(self, x0: torch.Tensor, txt: torch.Tensor, cond: torch.Tensor, t: torch.Tensor,
@@ -210,14 +344,24 @@ class Trainer:
         flat.zero_grad()
         params = stack.lora_parameters()
         reducer = dp.BucketReducer(flat.grads, self.group)
-        if self.grad_checkpointing:
-            # a block's gradients are final once its replayed backward is enqueued: their all-reduce
-            # starts there and overlaps the replay of the blocks below it
-            def after_block(i: int) -> None:
-                if reducer.world > 1:
-                    flat.gather_autograd_grads(stack.block_slices[i])
-                    reducer.reduce_slice(*stack.block_slices[i])
+        # a block's gradients are final once its replayed backward is enqueued: their all-reduce
+        # starts there and overlaps the replay of the blocks below it
+        def after_block(i: int) -> None:
+            if reducer.world > 1:
+                flat.gather_autograd_grads(stack.block_slices[i])
+                reducer.reduce_slice(*stack.block_slices[i])
 
+        if self.graphs:
+            key = (tuple(state.shape), tuple(cond.shape))
+            sweep = self._sweeps.get(key)
+            if sweep is None:
+                sweep = GraphedSweep(stack, state.shape, cond.shape, target.shape)
+                sweep.capture()
+                self._sweeps[key] = sweep
+            stack.set_cond(sweep.cond)
+            loss_dev = sweep.run(state, cond, target, self.scaler.loss_scale, after_block)
+            flat.gather_autograd_grads()
+        elif self.grad_checkpointing:
             loss, _ = checkpointed_step(stack.block_callables(), state, head, params, self.scaler.loss_scale,
                                         keep_existing_grads=True, after_block=after_block)
             flat.gather_autograd_grads()
@@ -235,6 +379,8 @@ class Trainer:
         # advance the loss-scale state (where the reference reads its |g| sum back)
         self.optim.step(self.lr, grad_scale=scale / self.scaler.loss_scale, skip_flag=flat.flag)
         flat.refresh_mirrors()  # the factors changed: all bf16 operand mirrors in one batched launch
+        if self.graphs:
+            loss = float(loss_dev)
         finite, _ = dp.consensus_step(self.scaler, flat.flag)
         if not finite:
             self.optim.steps -= 1  # a skipped update does not advance the bias-correction clock

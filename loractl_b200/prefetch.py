@@ -47,6 +47,22 @@ class BlockWeightPrefetcher:
     def slot(i: int) -> int:
         return i & 1
 
+    def fill(self, i: int, stream) -> None:
+        """Block i's copies rebuilt into its slot on `stream`, with no ordering of its own (the caller
+        orders `stream` against the readers of the slot's previous content and of the new one)."""
+        s = self.slot(i)
+        old = self.occupant[s]
+        if old is not None and old != i:
+            for w in self.weights[old]:
+                w.detach_bf16_copy()
+            self.ready.pop(old, None)
+        arena = self.arenas[s]
+        with torch.cuda.stream(stream):
+            for w, off in zip(self.weights[i], self.offsets[i]):
+                w.attach_bf16_copy(arena[off:off + w.d_out * w.d_in])
+        self.occupant[s] = i
+        self.fills += 1
+
     def prefetch(self, i: int) -> None:
         """Starts building block i's copies on the side stream unless they are in place already."""
         if i < 0 or i >= len(self.weights) or self.occupant[self.slot(i)] == i:
