@@ -368,9 +368,13 @@ def run_ours(args):
             raise SystemExit("--compute fp8 needs a scaled-fp8 workload (cfg2)")
         wq.prepare_fp8_backward()
 
+    # the factors' bf16 operand mirror: a trainer refreshes it once after each optimizer update
+    # (`lq_lora_mirror_update`), outside forward and backward; A and B do not change here
+    mirror = Q.lora_mirror(a, b)
+
     def step(xd, dyd):
-        y, h = Q.linear_fwd_raw(wq, xd, a, b, s, fp8_compute=fp8c)
-        dx, _, _ = Q.linear_bwd_raw(wq, dyd, xd, h, a, b, s, da_out=da, db_out=db, fp8_compute=fp8c)
+        y, h = Q.linear_fwd_raw(wq, xd, a, b, s, fp8_compute=fp8c, mirror=mirror)
+        dx, _, _ = Q.linear_bwd_raw(wq, dyd, xd, h, a, b, s, da_out=da, db_out=db, fp8_compute=fp8c, mirror=mirror)
         if world > 1:
             dist.all_reduce(bucket)  # the only exchange of the data-parallel path
         return y, dx
@@ -431,8 +435,8 @@ def run_ours(args):
         return g
 
     def local_step(f8):
-        y_, h_ = Q.linear_fwd_raw(wq, x, a, b, s, fp8_compute=f8)
-        Q.linear_bwd_raw(wq, dy, x, h_, a, b, s, da_out=da, db_out=db, fp8_compute=f8)
+        y_, h_ = Q.linear_fwd_raw(wq, x, a, b, s, fp8_compute=f8, mirror=mirror)
+        Q.linear_bwd_raw(wq, dy, x, h_, a, b, s, da_out=da, db_out=db, fp8_compute=f8, mirror=mirror)
 
     use_graph = not args.no_graph
     if use_graph:
@@ -575,7 +579,8 @@ def run_ours(args):
                 "sites": {key: {"stream_bytes_per_site": v["stream_bytes_per_site"], "distinct_sites": v["sites"],
                                 "by_tokens": {t: {"site_us": d["site_us"], "gbs": d["site_stream_gbs"],
                                                   "frac": d["frac_of_hbm"], "grouped4_site_us": d["grouped4_site_us"],
-                                                  "grouped4_frac": d["grouped4_frac_of_hbm"]}
+                                                  "grouped4_frac": d["grouped4_frac_of_hbm"],
+                                                  "bwd_site_us": d["bwd_site_us"], "bwd_frac": d["bwd_frac_of_hbm"]}
                                               for t, d in v["by_tokens"].items()}}
                           for key, v in sres.items()},
             }
@@ -640,7 +645,8 @@ def run_ours(args):
             "config": {"workload": wl, "scheme": scheme, "d_in": k, "d_out": m, "rank": r, "alpha": alpha,
                        "tokens_per_gpu": n, "parallelism": f"dp{world}",
                        "l2": f"inputs larger than L2 (X+dY+Y+dX = {4 * n * (k + m) / 1e6:.0f} MB per step vs 126 MB)",
-                       "launch": "eager" if args.no_graph else "CUDA graph of the step, replayed"},
+                       "launch": "eager" if args.no_graph else "CUDA graph of the step, replayed",
+                       "lora_mirror": "bf16 operand mirror of A, B built once before the timed region"},
             "roofline": roofline,
             "cpu_baseline": {"value": cpu_tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                              "sample": f"fwd+bwd on {min(n, 1024)} of {n} tokens, 3 reps, numpy f32"},
@@ -787,11 +793,26 @@ def measure_stream(dev, reps: int, token_counts=(1, 8, 16, 64)):
 
             site_ms = replay_time(chain)
             grouped_ms = replay_time(chain_grouped) if (scheme == "int4" and n <= 16) else None
+            # the backward of the same sites (dX through the packed stream, dA, dB): int4, <= 16 tokens
+            bwd_ms = None
+            if scheme == "int4" and n <= 16:
+                dy = torch.randn((n, m), generator=g, device=dev).to(torch.bfloat16)
+                _, h_keep = Q.linear_fwd_raw(weights[0], x, a, b, s)
+
+                def chain_bwd():
+                    out = None
+                    for wq in weights:
+                        out = Q.linear_bwd_raw(wq, dy, x, h_keep, a, b, s)
+                    return out
+
+                bwd_ms = replay_time(chain_bwd)
             results[str(n)] = {
                 "site_us": site_ms * 1e3, "site_stream_gbs": stream_bytes / (site_ms * 1e-3) / 1e9,
                 "frac_of_hbm": stream_bytes / (site_ms * 1e-3) / 1e9 / hbm,
                 "grouped4_site_us": grouped_ms * 1e3 if grouped_ms else None,
                 "grouped4_frac_of_hbm": stream_bytes / (grouped_ms * 1e-3) / 1e9 / hbm if grouped_ms else None,
+                "bwd_site_us": bwd_ms * 1e3 if bwd_ms else None,
+                "bwd_frac_of_hbm": stream_bytes / (bwd_ms * 1e-3) / 1e9 / hbm if bwd_ms else None,
                 "fused_kernel_us": fused_ms * 1e3,
                 "fused_kernel_stream_gbs": stream_bytes / (fused_ms * 1e-3) / 1e9,
                 "by_kernel_us": {kk: v[0] / max(v[1], 1) * 1e3 for kk, v in kinds.items() if v[1]},

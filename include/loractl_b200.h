@@ -203,7 +203,10 @@ int lq_linear_fwd(const lq_weight_t* w, const void* X, int64_t n_tokens, int dty
  * dY, X, dX have element type `dtype`; H is the f32 [N, r] saved by the forward
  * (NULL: recomputed as X . A); dA, dB are f32 and are OVERWRITTEN unless
  * `accumulate` is non-zero (then added to, for a flat gradient bucket).
- * dX may be NULL (input needs no gradient); dA/dB may be NULL when rank == 0. */
+ * dX may be NULL (input needs no gradient); dA/dB may be NULL when rank == 0.
+ * Routes (bf16): int4 weights with quant block 64 at <= 16 tokens read the packed weight once and
+ * convert it in registers (no bf16 image of W^T is written; dH, dA, dB are formed by the same two
+ * launches); everything else dequantises into the workspace, or reads an attached bf16 copy. */
 int lq_linear_bwd(const lq_weight_t* w, const void* dY, const void* X, const float* H,
                   int64_t n_tokens, int dtype, const float* A, const float* B, int rank,
                   float scaling, void* dX, float* dA, float* dB, int accumulate,

@@ -24,7 +24,37 @@ struct GemmParams {
     int col_scale_bcast = 0;
     int tma_store = 0;  // bf16 output leaves through shared memory and TMA tensor stores (full 64-byte row pieces)
     int group_m = 0;    // m-tiles per raster group (0 = 16)
+    // CTA-pair kernel: the tiles from `tail_first` on (a thin last round of the persistent grid) are cut
+    // into `tail_splits` ranges of k-blocks, one work item each, so that the round fills the machine;
+    // those items write f32 partial tiles to `tail_part` ([tile - tail_first][split][256][BLOCK_N]) and a
+    // second launch sums them in a fixed order.  tail_splits <= 1: no tile is cut.
+    int tail_first = 0, tail_splits = 1;
+    float* tail_part = nullptr;
 };
+
+// Work item -> (tile, k-block range) with the last tiles cut along k.  `slot` >= 0 is the partial-tile
+// slot a cut item writes, -1 for a whole tile.
+__device__ __forceinline__ void pair_item(const GemmParams& p, int item, int kb_total, int& tile, int& kb_begin,
+                                          int& kb_end, int& slot) {
+    const int tiles = p.m_tiles * p.n_tiles;
+    const int tail_first = p.tail_splits > 1 ? p.tail_first : tiles;
+    if (item < tail_first) {
+        tile = item;
+        kb_begin = 0;
+        kb_end = kb_total;
+        slot = -1;
+    } else {
+        const int q = item - tail_first, z = q % p.tail_splits;
+        tile = tail_first + q / p.tail_splits;
+        kb_begin = (int)(((long long)kb_total * z) / p.tail_splits);
+        kb_end = (int)(((long long)kb_total * (z + 1)) / p.tail_splits);
+        slot = q;
+    }
+}
+__device__ __forceinline__ int pair_num_items(const GemmParams& p) {
+    const int tiles = p.m_tiles * p.n_tiles;
+    return p.tail_splits > 1 ? p.tail_first + (tiles - p.tail_first) * p.tail_splits : tiles;
+}
 
 template <int BLOCK_N>
 struct Cfg {

@@ -404,7 +404,7 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
     const uint32_t tmem_base = *tmem_slot;
 
     const int kb_total = p.kb0 + p.kb1;
-    const int num_items = p.m_tiles * p.n_tiles;  // m_tiles counts 256-row pair tiles here
+    const int num_items = pair_num_items(p);  // m_tiles counts 256-row pair tiles here; the last tiles may be cut along k
     const int cid = (int)(blockIdx.x >> 1), ncl = (int)(gridDim.x >> 1);
 
     if (warp == 0) {
@@ -414,9 +414,10 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
             uint32_t phase = 0;
             bool ok = true;
             for (int item = cid; ok && item < num_items; item += ncl) {
-                int m_tile, n_tile, z;
-                item_coords(p, item, m_tile, n_tile, z);
-                for (int kb = 0; kb < kb_total; ++kb) {
+                int m_tile, n_tile, z, tile, kb_begin, kb_end, slot;
+                pair_item(p, item, kb_total, tile, kb_begin, kb_end, slot);
+                item_coords(p, tile, m_tile, n_tile, z);
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait(smem_u32(&empty[s]), phase ^ 1u, abort_flag, p.status, 51)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&full[s]);
                     if (leader) mbar_expect_tx(bar, 2 * (C::A_BYTES + C::B_BYTES));
@@ -457,7 +458,9 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
                 if (!mbar_wait(smem_u32(&tempty[acc]), acc_phase ^ 1u, abort_flag, p.status, 52)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BLOCK_N);
-                for (int kb = 0; kb < kb_total; ++kb) {
+                int tile, kb_begin, kb_end, slot;
+                pair_item(p, item, kb_total, tile, kb_begin, kb_end, slot);
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait(smem_u32(&full[s]), phase, abort_flag, p.status, 53)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_lo = a_lo0 + (uint32_t)s * (C::A_BYTES >> 4);
@@ -466,18 +469,18 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             mma2_f8(tmem_d, desc_join(a_lo + k * 2u, d_hi), desc_join(b_lo + k * 2u, d_hi), idesc8,
-                                    (kb > 0 || k > 0) ? 1u : 0u);
+                                    (kb > kb_begin || k > 0) ? 1u : 0u);
                     } else if (B_MN && kb < p.kb0) {
                         const uint32_t bm_lo = b_lo0_mn + (uint32_t)s * (C::B_BYTES >> 4);
 #pragma unroll
                         for (int k = 0; k < BK / 16; ++k)  // 16 reduction rows of 128 bytes per step
                             mma2_f16(tmem_d, desc_join(a_lo + k * 2u, d_hi), desc_join(bm_lo + k * 128u, d_hi), idesc_mn,
-                                     (kb > 0 || k > 0) ? 1u : 0u);
+                                     (kb > kb_begin || k > 0) ? 1u : 0u);
                     } else {
 #pragma unroll
                         for (int k = 0; k < BK / 16; ++k)
                             mma2_f16(tmem_d, desc_join(a_lo + k * 2u, d_hi), desc_join(b_lo + k * 2u, d_hi), idesc,
-                                     (kb > 0 || k > 0) ? 1u : 0u);
+                                     (kb > kb_begin || k > 0) ? 1u : 0u);
                     }
                     mma2_commit_mc(smem_u32(&empty[s]), 3);  // frees the stage in both CTAs
                     if (++s == STAGES) { s = 0; phase ^= 1u; }
@@ -495,10 +498,31 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
         uint32_t acc_phase = 0;
         bool ok = true;
         for (int item = cid; ok && item < num_items; item += ncl) {
-            int m_tile, n_tile, z;
-            item_coords(p, item, m_tile, n_tile, z);
+            int m_tile, n_tile, z, tile, kb_begin, kb_end, slot;
+            pair_item(p, item, kb_total, tile, kb_begin, kb_end, slot);
+            item_coords(p, tile, m_tile, n_tile, z);
             if (!mbar_wait(smem_u32(&tfull[acc]), acc_phase, abort_flag, p.status, 54)) { ok = false; break; }
             tc_fence_after();
+            if (slot >= 0) {
+                // a k-range of a cut tile: the raw f32 accumulator goes to its partial slot (scales, bias
+                // and the bf16 rounding are applied once, by the launch that sums the slots)
+                float* dst = p.tail_part + ((size_t)slot * 256 + (size_t)((int)rank * BM + quarter * 32 + lane)) * BLOCK_N;
+#pragma unroll 1
+                for (int c = 0; c < BLOCK_N / 64; ++c) {
+                    uint32_t r[32];
+                    const int cc = chalf * (BLOCK_N / 2) + c * 32;
+                    tmem_ld_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N + cc), r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        *(uint4*)(dst + cc + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                }
+                tc_fence_before();
+                if (leader) mbar_arrive(smem_u32(&tempty[acc]));
+                else mbar_arrive_leader(smem_u32(&tempty[acc]));
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+                continue;
+            }
             const int row0 = m_tile * 256 + (int)rank * BM + quarter * 32;
             const int row = row0 + lane;
             const float rs = (p.row_scale && row < p.Mg) ? p.row_scale[row] : 1.f;
@@ -569,6 +593,46 @@ umma_gemm2_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc2(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// Second launch of a pair GEMM whose last tiles were cut along k: sums the partial slots of each cut
+// tile in a fixed order, applies what the epilogue would have (scales, bias) and stores bf16.
+template <int BLOCK_N>
+__global__ void __launch_bounds__(256) pair_tail_reduce_kernel(GemmParams p) {
+    constexpr int CG = BLOCK_N / 4;        // 4-column groups per row
+    constexpr int RPB = 256 / CG;          // rows per block (BLOCK_N 256: 4, 192: 5 with idle threads)
+    const int t = (int)threadIdx.x;
+    if (t >= RPB * CG) return;
+    const int blocks_per_tile = (256 + RPB - 1) / RPB;
+    const int j = (int)blockIdx.x / blocks_per_tile;
+    const int r = ((int)blockIdx.x - j * blocks_per_tile) * RPB + t / CG;
+    const int c = (t % CG) * 4;
+    if (r >= 256) return;
+    int m_tile, n_tile, z;
+    item_coords(p, p.tail_first + j, m_tile, n_tile, z);
+    const int row = m_tile * 256 + r, col = n_tile * BLOCK_N + c;
+    if (row >= p.Mg || col >= p.Ng) return;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int q = 0; q < p.tail_splits; ++q) {
+        const float4 a = *(const float4*)(p.tail_part + (((size_t)j * p.tail_splits + q) * 256 + r) * BLOCK_N + c);
+        v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+    }
+    float e[4] = {v.x, v.y, v.z, v.w};
+    const float rs = p.row_scale ? p.row_scale[row] : 1.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (col + i >= p.Ng) continue;
+        if (p.col_scale) e[i] *= rs * p.col_scale[p.col_scale_bcast ? 0 : col + i];
+        else if (p.row_scale) e[i] *= rs;
+        if (p.bias) e[i] += p.bias[col + i];
+    }
+    __nv_bfloat16* out = (__nv_bfloat16*)p.C + (size_t)row * p.ldc + col;
+    if (col + 3 < p.Ng) {  // Ng % 8 == 0 on this path: a 4-column group is whole or absent, kept general anyway
+        __nv_bfloat162 lo = __floats2bfloat162_rn(e[0], e[1]), hi = __floats2bfloat162_rn(e[2], e[3]);
+        *(uint2*)out = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+    } else {
+        for (int i = 0; i < 4 && col + i < p.Ng; ++i) out[i] = __float2bfloat16(e[i]);
     }
 }
 
@@ -843,6 +907,17 @@ std::atomic<int> g_bwd_mn{[] {
     return e ? atoi(e) : 0;
 }()};
 
+// "tail_split" (LQ_TAIL_SPLIT=0 to switch off): cut the tiles of a thin last round along k
+std::atomic<int> g_tail_split{[] {
+    const char* e = getenv("LQ_TAIL_SPLIT");
+    return e ? atoi(e) : 1;
+}()};
+constexpr int kMaxTailSplits = 8;
+constexpr int kMinTailKBlocks = 96;
+// f32 partial tiles of the cut round: (tiles of the round) x splits <= kTailSlots slots of 256 x 256
+constexpr int kTailSlots = 80;
+constexpr size_t kTailWsBytes = (size_t)kTailSlots * 256 * 256 * 4;
+
 bool pair_enabled() {
     static const bool on = [] {
         const char* e = getenv("LQ_GEMM_1CTA");
@@ -855,7 +930,7 @@ bool pair_enabled() {
 template <int BLOCK_N, bool F8, bool B_MN = false>
 void launch_gemm_pair(const Operand& a0, const Operand& b0, int64_t K0, const Operand* a1, const Operand* b1, int64_t K1,
                       __nv_bfloat16* Cout, int64_t ldc, int64_t Mg, int64_t Ng, const float* bias, cudaStream_t st,
-                      EpiScales sc = EpiScales()) {
+                      EpiScales sc = EpiScales(), float* tail_ws = nullptr) {
     using C = Cfg2<BLOCK_N>;
     int dev;
     LQ_CUDA(cudaGetDevice(&dev));
@@ -905,10 +980,35 @@ void launch_gemm_pair(const Operand& a0, const Operand& b0, int64_t K0, const Op
         }
         pairs = pairs_by_dev[dev];
     }
-    const int grid = 2 * (int)std::min<long long>(items, pairs);
-    LqProf prof(LQ_K_GEMM_MAIN, st);
-    kern<<<grid, kThreads, C::SMEM, st>>>(tA0, tB0, tA1, tB1, tC, p);
-    LQ_CUDA(cudaGetLastError());
+    // A thin last round (at most half the pairs busy) is cut along k so that it fills the machine:
+    // config 2's backward is 384 tiles on 74 pairs = 5.19 rounds, which ran as 6.
+    const int rem = items > pairs ? (int)(items % pairs) : 0;
+    const int kb_total = p.kb0 + p.kb1;
+    // Worth it only for long reductions: the cut saves (1 - 1/splits) of a round (0.28 us per k-block)
+    // and costs the summing launch plus the overlap the idle pairs used to give the dA contraction
+    // (measured: config 2's dX GEMM 0.41 -> 0.36 ms, whole step -1..2 %; a 49-k-block GEMM loses 7 us)
+    if (tail_ws && g_tail_split.load() != 0 && rem > 0 && 2 * rem <= pairs && kb_total >= kMinTailKBlocks) {
+        const int splits = std::min(std::min(pairs / rem, kTailSlots / rem), std::min(kMaxTailSplits, kb_total / 8));
+        if (splits >= 2) {
+            p.tail_first = (int)(items - rem);
+            p.tail_splits = splits;
+            p.tail_part = tail_ws;
+        }
+    }
+    const long long work = p.tail_splits > 1 ? (long long)p.tail_first + (long long)rem * p.tail_splits : items;
+    const int grid = 2 * (int)std::min<long long>(work, pairs);
+    {
+        LqProf prof(LQ_K_GEMM_MAIN, st);
+        kern<<<grid, kThreads, C::SMEM, st>>>(tA0, tB0, tA1, tB1, tC, p);
+        LQ_CUDA(cudaGetLastError());
+    }
+    if (p.tail_splits > 1) {
+        LqProf prof(LQ_K_REDUCE, st);
+        constexpr int RPB = 256 / (BLOCK_N / 4);
+        const int blocks = rem * ((256 + RPB - 1) / RPB);
+        pair_tail_reduce_kernel<BLOCK_N><<<blocks, 256, 0, st>>>(p);
+        LQ_CUDA(cudaGetLastError());
+    }
 }
 
 // Tile width for the pair kernel.  Measured on config 2's backward (512 tiles of 192 columns in 7
@@ -919,13 +1019,18 @@ inline int forced_pair_bn() {
     static const int v = [] { const char* e = getenv("LQ_PAIR_BN"); return e ? atoi(e) : 0; }();
     return v;
 }
-inline int pair_block_n(int64_t Mg, int64_t Ng, int sm_count) {
+inline int pair_block_n(int64_t Mg, int64_t Ng, int sm_count, int kb_total = 0) {
     if (forced_pair_bn() == 192 || forced_pair_bn() == 256) return forced_pair_bn();
     const int64_t pairs = std::max(1, sm_count / 2);
     auto cost = [&](int bn) {
         const int64_t tiles = ((Mg + 255) / 256) * ((Ng + bn - 1) / bn);
-        const int64_t rounds = (tiles + pairs - 1) / pairs;
-        return (double)rounds * (bn == 256 ? 1.0 : 0.95);
+        const int64_t rem = tiles > pairs ? tiles % pairs : 0;
+        double rounds = (double)((tiles + pairs - 1) / pairs);
+        // a last round that is at most half full is cut along k (launch_gemm_pair): it costs its share
+        // of a round plus the launch that sums the partial tiles
+        if (g_tail_split.load() != 0 && rem > 0 && 2 * rem <= pairs && kb_total >= kMinTailKBlocks)
+            rounds += -1.0 + 1.0 / (double)std::min<int64_t>(pairs / rem, kMaxTailSplits) + 0.3;
+        return rounds * (bn == 256 ? 1.0 : 0.95);
     };
     return cost(192) < cost(256) ? 192 : 256;
 }
@@ -952,6 +1057,7 @@ struct TcWs {
     float* part;          // split partials
     float* part2;         // split partials of the contractions that run on the side stream (dB, recomputed H)
     __nv_bfloat16* pdown2; // bwd, H recomputed: A^T [r, K]
+    float* tail;          // f32 partial tiles of a frozen GEMM whose last round is cut along k
     size_t bytes;
 };
 
@@ -966,6 +1072,7 @@ TcWs carve_tc(const lq_weight* w, int64_t N, int r, void* base, int sm_count) {
     };
     TcWs t{};
     t.wscr = (__nv_bfloat16*)take(M * K * 2);
+    t.tail = N >= 256 ? (float*)take(kTailWsBytes) : nullptr;
     if (r > 0) {
         t.Hf = (float*)take((size_t)N * r * 4);
         t.dHf = (float*)take((size_t)N * r * 4);
@@ -1085,16 +1192,19 @@ __global__ void __launch_bounds__(256) lora_mirror_kernel(const float* __restric
 
 template <typename OutT>
 void main_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand* a1, const Operand* b1, int64_t K1,
-               OutT* Cout, int64_t ldc, int64_t Mg, int64_t Ng, const float* bias, int sm_count, cudaStream_t st) {
+               OutT* Cout, int64_t ldc, int64_t Mg, int64_t Ng, const float* bias, int sm_count, cudaStream_t st,
+               float* tail_ws = nullptr) {
     // Tile width: 128 x 256 is the efficient shape (96 B/clk of operand traffic per SM); 128 x 128
     // needs 128 B/clk and measured 1.5x slower per FLOP.  128 x 192 sits close to 256 and is taken
     // when it fills the last wave of the persistent grid markedly better.
     if constexpr (sizeof(OutT) == 2) {
         if (pair_enabled() && Mg >= 256 && Ng > 192 && sm_count >= 2) {  // the frozen GEMMs proper: CTA pairs
-            if (pair_block_n(Mg, Ng, sm_count) == 256)
-                launch_gemm_pair<256, false>(a0, b0, K0, a1, b1, K1, (__nv_bfloat16*)Cout, ldc, Mg, Ng, bias, st);
+            if (pair_block_n(Mg, Ng, sm_count, tail_ws ? (int)((K0 + BK - 1) / BK + (a1 ? (K1 + BK - 1) / BK : 0)) : 0) == 256)
+                launch_gemm_pair<256, false>(a0, b0, K0, a1, b1, K1, (__nv_bfloat16*)Cout, ldc, Mg, Ng, bias, st,
+                                             EpiScales(), tail_ws);
             else
-                launch_gemm_pair<192, false>(a0, b0, K0, a1, b1, K1, (__nv_bfloat16*)Cout, ldc, Mg, Ng, bias, st);
+                launch_gemm_pair<192, false>(a0, b0, K0, a1, b1, K1, (__nv_bfloat16*)Cout, ldc, Mg, Ng, bias, st,
+                                             EpiScales(), tail_ws);
             return;
         }
     }
@@ -1265,6 +1375,7 @@ struct W8Ws {
     float* part;
     float* part2;          // partials of the contractions on the side stream (dB, recomputed H)
     __nv_bfloat16* pdown2; // bwd, H recomputed: A^T [r, K]
+    float* tail;           // f32 partial tiles of a frozen GEMM whose last round is cut along k
     size_t bytes;
 };
 
@@ -1280,6 +1391,7 @@ W8Ws carve_w8(const lq_weight* w, int64_t N, int r, void* base) {
     W8Ws t{};
     t.q8 = (uint8_t*)take((size_t)N * std::max(M, K));
     t.srow = (float*)take((size_t)N * 4);
+    t.tail = N >= 256 ? (float*)take(kTailWsBytes) : nullptr;
     if (r > 0) {
         t.Hf = (float*)take((size_t)N * r * 4);
         t.dHf = (float*)take((size_t)N * r * 4);
@@ -1311,7 +1423,7 @@ void quant_rows(const void* x, int64_t N, int64_t C, const float* colmul, uint8_
 
 void main_gemm_f8(const Operand& a0, const Operand& b0, int64_t K0, const Operand* a1, const Operand* b1, int64_t K1,
                   __nv_bfloat16* Cout, int64_t ldc, int64_t Mg, int64_t Ng, const float* bias, const EpiScales& sc,
-                  int sm_count, cudaStream_t st) {
+                  int sm_count, cudaStream_t st, float* tail_ws = nullptr) {
     const int64_t m_tiles = (Mg + BM - 1) / BM;
     auto waves_eff = [&](int bn) {
         const int64_t tiles = m_tiles * ((Ng + bn - 1) / bn);
@@ -1321,10 +1433,10 @@ void main_gemm_f8(const Operand& a0, const Operand& b0, int64_t K0, const Operan
     };
     using T = __nv_bfloat16;
     if (pair_enabled() && Mg >= 256 && Ng > 192 && sm_count >= 2) {
-        if (pair_block_n(Mg, Ng, sm_count) == 256)
-            launch_gemm_pair<256, true>(a0, b0, K0, a1, b1, K1, Cout, ldc, Mg, Ng, bias, st, sc);
+        if (pair_block_n(Mg, Ng, sm_count, tail_ws ? (int)((K0 + 127) / 128 + (a1 ? (K1 + BK - 1) / BK : 0)) : 0) == 256)
+            launch_gemm_pair<256, true>(a0, b0, K0, a1, b1, K1, Cout, ldc, Mg, Ng, bias, st, sc, tail_ws);
         else
-            launch_gemm_pair<192, true>(a0, b0, K0, a1, b1, K1, Cout, ldc, Mg, Ng, bias, st, sc);
+            launch_gemm_pair<192, true>(a0, b0, K0, a1, b1, K1, Cout, ldc, Mg, Ng, bias, st, sc, tail_ws);
         return;
     }
     if (Ng <= 128)
@@ -1424,6 +1536,7 @@ size_t lq_tc_mirror_bytes(int64_t K, int64_t M, int r) { return r > 0 ? carve_mi
 
 bool lq_tc_option_set(const char* name, int value) {
     if (std::strcmp(name, "bwd_mn") == 0) { g_bwd_mn = value; return true; }
+    if (std::strcmp(name, "tail_split") == 0) { g_tail_split = value; return true; }
     return false;
 }
 
@@ -1522,7 +1635,7 @@ void lq_tc_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, con
             return;
         }
         if (!cached) lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, st);
-        main_gemm<__nv_bfloat16>(a0, b0, K, nullptr, nullptr, 0, (__nv_bfloat16*)Y, M, N, M, w->bias, ctx.sm_count, st);
+        main_gemm<__nv_bfloat16>(a0, b0, K, nullptr, nullptr, 0, (__nv_bfloat16*)Y, M, N, M, w->bias, ctx.sm_count, st, t.tail);
         return;
     }
     const int EXT = ext_width(r);
@@ -1548,7 +1661,7 @@ void lq_tc_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, con
         return;
     }
     Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
-    main_gemm<__nv_bfloat16>(a0, b0, K, &a1, &b1, EXT, (__nv_bfloat16*)Y, M, N, M, w->bias, ctx.sm_count, st);
+    main_gemm<__nv_bfloat16>(a0, b0, K, &a1, &b1, EXT, (__nv_bfloat16*)Y, M, N, M, w->bias, ctx.sm_count, st, t.tail);
 }
 
 void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H, int64_t N, const float* A,
@@ -1579,10 +1692,11 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
             lq_w4_gemm(w, 1, dY, M, nullptr, 0, nullptr, 0, 0, dX, K, N, nullptr, st);
         } else if (dX && (cached || mn_scratch)) {
             if (mn_scratch) lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, st);
-            launch_gemm_pair<256, false, true>(a0, bmn, M, nullptr, nullptr, 0, (__nv_bfloat16*)dX, K, N, K, nullptr, st);
+            launch_gemm_pair<256, false, true>(a0, bmn, M, nullptr, nullptr, 0, (__nv_bfloat16*)dX, K, N, K, nullptr, st,
+                                               EpiScales(), t.tail);
         } else if (dX) {
             lq_launch_dequant(w, t.wscr, LQ_BF16, M, 1, st);  // W^T [K, M]
-            main_gemm<__nv_bfloat16>(a0, b0, M, nullptr, nullptr, 0, (__nv_bfloat16*)dX, K, N, K, nullptr, ctx.sm_count, st);
+            main_gemm<__nv_bfloat16>(a0, b0, M, nullptr, nullptr, 0, (__nv_bfloat16*)dX, K, N, K, nullptr, ctx.sm_count, st, t.tail);
         }
         return;
     }
@@ -1626,10 +1740,11 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
             lq_w4_gemm(w, 1, dY, M, t.ext_a, EXT, t.pext, EXT, EXT, dX, K, N, nullptr, st);
         } else if (cached || mn_scratch) {
             Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
-            launch_gemm_pair<256, false, true>(a0, bmn, M, &a1, &b1, EXT, (__nv_bfloat16*)dX, K, N, K, nullptr, st);
+            launch_gemm_pair<256, false, true>(a0, bmn, M, &a1, &b1, EXT, (__nv_bfloat16*)dX, K, N, K, nullptr, st,
+                                               EpiScales(), t.tail);
         } else {
             Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
-            main_gemm<__nv_bfloat16>(a0, b0, M, &a1, &b1, EXT, (__nv_bfloat16*)dX, K, N, K, nullptr, ctx.sm_count, st);
+            main_gemm<__nv_bfloat16>(a0, b0, M, &a1, &b1, EXT, (__nv_bfloat16*)dX, K, N, K, nullptr, ctx.sm_count, st, t.tail);
         }
     }
     if (dA)  // dA[K, r] = X^T . dH
@@ -1668,7 +1783,7 @@ void lq_w8a8_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, c
     Operand a0{t.q8, false, K}, b0{w->packed, false, K};
     if (r == 0) {
         quant_rows(X, N, K, nullptr, t.q8, t.srow, st);  // X -> e4m3 with one scale per token
-        main_gemm_f8(a0, b0, K, nullptr, nullptr, 0, (__nv_bfloat16*)Y, M, N, M, w->bias, sc, ctx.sm_count, st);
+        main_gemm_f8(a0, b0, K, nullptr, nullptr, 0, (__nv_bfloat16*)Y, M, N, M, w->bias, sc, ctx.sm_count, st, t.tail);
         return;
     }
     const int EXT = ext_width(r);
@@ -1685,7 +1800,7 @@ void lq_w8a8_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, c
     fj.wait(0);
     // Y = (X8 . W8^T + ext) * s_x[n] * s_w[m] + bias
     Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
-    main_gemm_f8(a0, b0, K, &a1, &b1, EXT, (__nv_bfloat16*)Y, M, N, M, w->bias, sc, ctx.sm_count, st);
+    main_gemm_f8(a0, b0, K, &a1, &b1, EXT, (__nv_bfloat16*)Y, M, N, M, w->bias, sc, ctx.sm_count, st, t.tail);
 }
 
 void lq_w8a8_bwd(const lq_weight* w, const void* dY, const void* X, const float* H, int64_t N, const float* A,
@@ -1710,7 +1825,7 @@ void lq_w8a8_bwd(const lq_weight* w, const void* dY, const void* X, const float*
             const uint8_t* wt = ensure_transposed(w, st);
             quant_rows(dY, N, M, per_channel ? w->scales : nullptr, t.q8, t.srow, st);
             Operand a0{t.q8, false, M}, b0{wt, false, M};
-            main_gemm_f8(a0, b0, M, nullptr, nullptr, 0, (__nv_bfloat16*)dX, K, N, K, nullptr, sc, ctx.sm_count, st);
+            main_gemm_f8(a0, b0, M, nullptr, nullptr, 0, (__nv_bfloat16*)dX, K, N, K, nullptr, sc, ctx.sm_count, st, t.tail);
         }
         return;
     }
@@ -1742,7 +1857,7 @@ void lq_w8a8_bwd(const lq_weight* w, const void* dY, const void* X, const float*
         fj.wait(0);
         Operand a0{t.q8, false, M}, b0{wt, false, M};
         Operand a1{t.ext_a, false, EXT}, b1{t.pext, false, EXT};
-        main_gemm_f8(a0, b0, M, &a1, &b1, EXT, (__nv_bfloat16*)dX, K, N, K, nullptr, sc, ctx.sm_count, st);
+        main_gemm_f8(a0, b0, M, &a1, &b1, EXT, (__nv_bfloat16*)dX, K, N, K, nullptr, sc, ctx.sm_count, st, t.tail);
     }
     if (dA) {  // dA = X^T . dH with the plain bf16 dH
         const __nv_bfloat16* dh_plain = t.ext_a;

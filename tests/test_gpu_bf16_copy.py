@@ -53,8 +53,13 @@ def test_attached_copy_gives_the_same_results_without_a_dequant_pass(n, k, m, r,
     # MN-major read is a CTA-pair kernel, which wants at least one full 256-row tile)
     assert kinds.get("dequant", 0) == (0 if n >= 256 else 1), kinds
     assert torch.equal(got[0], ref[0]), "Y differs"
-    if not torch.equal(got[1], ref[1]):  # MN-major read of the same values: at most summation-order noise
-        assert reldev(host(got[1]), host(ref[1])) <= 1e-5
+    if not torch.equal(got[1], ref[1]):
+        # MN-major read of the same values; the two routes may tile differently (192- against 256-column
+        # tiles, a thin last round cut along k in one and not the other), which reorders f32 sums before
+        # the bf16 rounding: single roundings flip, nothing more
+        d = (got[1].float() - ref[1].float()).abs()
+        peak = float(ref[1].float().abs().max())
+        assert float(d.max()) <= 8e-3 * peak and float(d.mean()) <= 2e-4 * peak
     if r:
         assert torch.equal(got[2], ref[2]) and torch.equal(got[3], ref[3])
     wq.detach_bf16_copy()

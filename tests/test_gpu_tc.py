@@ -211,3 +211,59 @@ def test_more_tiles_than_cta_pairs_with_a_thin_last_round(n, k, m):
     assert reldev(host(da), oda) <= 8e-3 and reldev(host(db), odb) <= 8e-3
     y2, _ = Q.linear_fwd_raw(wq, xd, ad, bd, 1.5)
     assert torch.equal(y, y2)
+
+
+def _set_option(name, value):
+    from loractl_b200 import _lib as L
+
+    L.check(L.lib().lq_option_set(name.encode(), int(value)))
+
+
+@pytest.mark.parametrize("scheme", ["int4", "fp8", "fp8-native"])
+@pytest.mark.parametrize("n,k,m", [(2048, 6144, 3072), (2048, 3072, 6144), (2048, 12288, 3072)])
+def test_thin_last_round_cut_along_k_matches_the_uncut_gemm(n, k, m, scheme):
+    """A frozen GEMM with a long reduction (>= 96 k-blocks: d_in 6144 forward, d_out 6144 backward, d_in
+    12288 in native fp8) whose last round of the persistent pair grid is at most half full (96 tiles on
+    74 pairs here) has those tiles cut into k-ranges (f32 partial tiles, summed in a fixed order by a second launch).  Against the
+    same call with the cut switched off: equal up to the reordering of one f32 sum before the bf16
+    rounding; against the oracle: the usual band; and bit-identical when repeated."""
+    from loractl_b200 import quant as Q
+
+    w = seeded((m, k), 5, 0.02)
+    x = bf16_round(seeded((n, k), 6))
+    dy = bf16_round(seeded((n, m), 9))
+    a, b = seeded((k, 16), 7, 1.0 / np.sqrt(k)), seeded((16, m), 8, 0.01)
+    bias = seeded((m,), 10, 0.1)
+    if scheme == "int4":
+        wq = lb().quantize_linear_weight(dev(w), 4, 64)
+        dq = O.dequantize(*O.quantize(w, 64, 4), 64)
+    else:
+        wq = lb().fp8_quantize(dev(w), True)
+        dq = host(wq.dequantize())
+    wq.set_bias(dev(bias))
+    fp8c = scheme == "fp8-native"
+    xd, dyd, ad, bd = dev(x, torch.bfloat16), dev(dy, torch.bfloat16), dev(a), dev(b)
+
+    def run():
+        y, h = Q.linear_fwd_raw(wq, xd, ad, bd, 2.0, fp8_compute=fp8c)
+        dx, da, db = Q.linear_bwd_raw(wq, dyd, xd, h, ad, bd, 2.0, fp8_compute=fp8c)
+        lb().check_device_status()
+        return y, dx
+
+    try:
+        _set_option("tail_split", 0)
+        y0, dx0 = run()
+        _set_option("tail_split", 1)
+        y1, dx1 = run()
+        y2, dx2 = run()
+    finally:
+        _set_option("tail_split", 1)
+    assert torch.equal(y1, y2) and torch.equal(dx1, dx2)
+    for got, ref in ((y1, y0), (dx1, dx0)):
+        peak = float(ref.float().abs().max())
+        assert float((got.float() - ref.float()).abs().max()) <= 8e-3 * peak  # one bf16 ulp at the peak's binade
+        assert float((got.float() - ref.float()).abs().mean()) <= 2e-4 * peak
+    oy, _ = O.lora_linear_fwd(x, dq, a, b, 2.0, bias)
+    odx = O.lora_linear_bwd(dy, x, dq, a, b, 2.0)[0]
+    tol = 5e-2 if fp8c else 6e-3
+    assert reldev(host(y1), oy) <= tol and reldev(host(dx1), odx) <= tol

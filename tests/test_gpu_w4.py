@@ -37,9 +37,11 @@ def w4_on_for_these_tests():
     every size tried); these tests switch it on and restore the defaults afterwards."""
     set_option("w4", 1)
     set_option("w4_exact", 1)
+    set_option("tail_split", 0)  # the scratch path's k-cut of a thin last round changes its summation order
     yield
     set_option("w4", 0)
     set_option("w4_exact", 1)
+    set_option("tail_split", 1)
 
 
 def case(n, k, m, r, block, seed=5):
