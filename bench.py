@@ -687,10 +687,11 @@ def run_stream(args):
 
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
-    all_results, hbm = measure_stream(dev, max(args.steps, 10))
+    tokens = tuple(int(t) for t in args.stream_tokens.split(","))
+    all_results, hbm = measure_stream(dev, max(args.steps, 10), tokens, args.stream_only)
     r = 16
-    head = all_results["3072x12288-fp8"]
-    best = head["by_tokens"]["8"]
+    head = all_results.get("3072x12288-fp8") or next(iter(all_results.values()))
+    best = head["by_tokens"].get("8") or next(iter(head["by_tokens"].values()))
     line = {
         "metric": "packed-weight stream GB/s (cfg2 weight: scaled fp8 3072 -> 12288, forward, 8 tokens)",
         "value": best["site_stream_gbs"], "unit": "GB/s", "n_gpus": 1, "steps": max(args.steps, 10), "warmup": 3,
@@ -707,7 +708,7 @@ def run_stream(args):
     print(json.dumps(line))
 
 
-def measure_stream(dev, reps: int, token_counts=(1, 8, 16, 64)):
+def measure_stream(dev, reps: int, token_counts=(1, 8, 16, 64), only=None):
     """The three site shapes of the stream regime at the given token counts; returns
     ({site: {...}}, hbm peak GB/s).  Every rate carries its fraction of the measured HBM copy rate."""
     import torch
@@ -727,6 +728,8 @@ def measure_stream(dev, reps: int, token_counts=(1, 8, 16, 64)):
     # (d_out, d_in, sites): the cfg1 workload's 3072 x 3072 site, and the 3072 -> 12288 MLP up-projection
     # of configs 3/5 held as int4 (21.2 MB of packed weight per site)
     for m, k, sites, scheme in ((3072, 3072, 40, "int4"), (12288, 3072, 10, "int4"), (12288, 3072, 10, "fp8")):
+        if only and only != (f"{k}x{m}" if scheme == "int4" else f"{k}x{m}-fp8"):
+            continue  # `--stream-only`: one site shape, for a short profiler capture
         weights = []
         for _ in range(sites):
             w = torch.randn((m, k), generator=g, device=dev) * 0.02
@@ -1146,6 +1149,9 @@ def main():
     ap.add_argument("--weight-copies", nargs="?", const="resident", default="block", choices=["none", "resident", "block"],
                     help="--regime step: bf16 copies of the frozen weights. resident: of every weight, for the whole "
                          "run; block: two arenas of one block's copies, refilled one block ahead on a side stream")
+    ap.add_argument("--stream-tokens", default="1,8,16,64", help="--regime stream: token counts, comma separated")
+    ap.add_argument("--stream-only", default=None, choices=["3072x3072", "3072x12288", "3072x12288-fp8"],
+                    help="--regime stream: only this site shape (short runs for a profiler capture)")
     ap.add_argument("--no-extras", action="store_true",
                     help="tensor regime: skip the extra keys (int4_cfg1, stream, model_step) of the default line")
     ap.add_argument("--gpus", type=int, default=1)

@@ -982,7 +982,9 @@ void launch_gemm_pair(const Operand& a0, const Operand& b0, int64_t K0, const Op
     }
     // A thin last round (at most half the pairs busy) is cut along k so that it fills the machine:
     // config 2's backward is 384 tiles on 74 pairs = 5.19 rounds, which ran as 6.
-    const int rem = items > pairs ? (int)(items % pairs) : 0;
+    // ... and so is a GEMM whose ONLY round is at most half full (a 512-token site with a long
+    // reduction: 24 tiles for 74 pairs), all of whose tiles are then cut
+    const int rem = items > pairs ? (int)(items % pairs) : (int)items;
     const int kb_total = p.kb0 + p.kb1;
     // Worth it only for long reductions: the cut saves (1 - 1/splits) of a round (0.28 us per k-block)
     // and costs the summing launch plus the overlap the idle pairs used to give the dA contraction
@@ -1024,7 +1026,7 @@ inline int pair_block_n(int64_t Mg, int64_t Ng, int sm_count, int kb_total = 0) 
     const int64_t pairs = std::max(1, sm_count / 2);
     auto cost = [&](int bn) {
         const int64_t tiles = ((Mg + 255) / 256) * ((Ng + bn - 1) / bn);
-        const int64_t rem = tiles > pairs ? tiles % pairs : 0;
+        const int64_t rem = tiles > pairs ? tiles % pairs : tiles;
         double rounds = (double)((tiles + pairs - 1) / pairs);
         // a last round that is at most half full is cut along k (launch_gemm_pair): it costs its share
         // of a round plus the launch that sums the partial tiles

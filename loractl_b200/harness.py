@@ -351,6 +351,7 @@ class Trainer:
                 flat.gather_autograd_grads(stack.block_slices[i])
                 reducer.reduce_slice(*stack.block_slices[i])
 
+        torch.cuda.nvtx.range_push("lq.sweep")  # forward, head, reverse sweep (+ per-block all-reduce starts)
         if self.graphs:
             key = (tuple(state.shape), tuple(cond.shape))
             sweep = self._sweeps.get(key)
@@ -371,14 +372,19 @@ class Trainer:
             loss = float(loss_t.detach())
             flat.gather_autograd_grads()
             reducer.reduce_slice(0, flat.numel)
+        torch.cuda.nvtx.range_pop()
         # non-finite values survive the sum, so the flag is taken on the reduced gradients
+        torch.cuda.nvtx.range_push("lq.reduce_finish")
         scale = reducer.finish()
+        torch.cuda.nvtx.range_pop()
+        torch.cuda.nvtx.range_push("lq.optimizer")
         nonfinite_flag(flat.grads, flat.flag)
         dp.reduce_flag(flat.flag, self.group)
         # the optimizer reads the flag on the device and skips itself; the host reads it only to
         # advance the loss-scale state (where the reference reads its |g| sum back)
         self.optim.step(self.lr, grad_scale=scale / self.scaler.loss_scale, skip_flag=flat.flag)
         flat.refresh_mirrors()  # the factors changed: all bf16 operand mirrors in one batched launch
+        torch.cuda.nvtx.range_pop()
         if self.graphs:
             loss = float(loss_dev)
         finite, _ = dp.consensus_step(self.scaler, flat.flag)

@@ -116,9 +116,11 @@ class FlatAdapters:
     def gather_autograd_grads(self, only: Optional[tuple] = None) -> None:
         """If autograd accumulated into separate `.grad` tensors, fold them back into the bucket
         (`only` = (lo, hi): just the parameters whose segment starts inside that slice)."""
-        for p, o in zip(self._params, self.offsets):
-            if only is not None and not (only[0] <= o < only[1]):
-                continue
+        import bisect
+
+        lo = 0 if only is None else bisect.bisect_left(self.offsets, only[0])
+        hi = len(self.offsets) if only is None else bisect.bisect_left(self.offsets, only[1])
+        for p, o in zip(self._params[lo:hi], self.offsets[lo:hi]):
             if p.grad is not None and p.grad.data_ptr() != self.grads.data_ptr() + 4 * o:
                 self.grads[o:o + p.numel()].view(p.shape).copy_(p.grad)
                 p.grad = self.grads[o:o + p.numel()].view(p.shape)

@@ -220,11 +220,12 @@ def _set_option(name, value):
 
 
 @pytest.mark.parametrize("scheme", ["int4", "fp8", "fp8-native"])
-@pytest.mark.parametrize("n,k,m", [(2048, 6144, 3072), (2048, 3072, 6144), (2048, 12288, 3072)])
+@pytest.mark.parametrize("n,k,m", [(2048, 6144, 3072), (2048, 3072, 6144), (2048, 12288, 3072), (512, 12288, 3072),
+                                   (640, 3072, 12288)])
 def test_thin_last_round_cut_along_k_matches_the_uncut_gemm(n, k, m, scheme):
     """A frozen GEMM with a long reduction (>= 96 k-blocks: d_in 6144 forward, d_out 6144 backward, d_in
     12288 in native fp8) whose last round of the persistent pair grid is at most half full (96 tiles on
-    74 pairs here) has those tiles cut into k-ranges (f32 partial tiles, summed in a fixed order by a second launch).  Against the
+    74 pairs here), or whose only round is (a 512-token site: 24 tiles), has those tiles cut into k-ranges (f32 partial tiles, summed in a fixed order by a second launch).  Against the
     same call with the cut switched off: equal up to the reordering of one f32 sum before the bf16
     rounding; against the oracle: the usual band; and bit-identical when repeated."""
     from loractl_b200 import quant as Q
