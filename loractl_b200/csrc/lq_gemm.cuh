@@ -60,7 +60,10 @@ template <int BLOCK_N>
 struct Cfg {
     static constexpr uint32_t A_BYTES = BM * BK * 2;
     static constexpr uint32_t B_BYTES = BLOCK_N * BK * 2;
-    static constexpr int STAGES = (208 * 1024) / (A_BYTES + B_BYTES);
+    // 64-wide tiles belong to the memory-bound LoRA contractions that run BESIDE the dequantisation
+    // pass: six stages (144 KB, ample for the HBM latency) leave room for four of that pass's blocks
+    // per SM where eight stages left room for one
+    static constexpr int STAGES = BLOCK_N == 64 ? 6 : (208 * 1024) / (A_BYTES + B_BYTES);
     // 2 accumulator stages; the allocation must be a power of two >= 32 columns
     static constexpr uint32_t TMEM_COLS = BLOCK_N * 2 <= 128 ? 128 : (BLOCK_N * 2 <= 256 ? 256 : 512);
     static constexpr uint32_t STAGE_OUT = 8 * 2048;  // per epilogue warp: 32 rows x 64 bytes of bf16 output

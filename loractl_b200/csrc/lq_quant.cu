@@ -5,6 +5,7 @@
 //   scale = absmax / qmax            (f32, IEEE division)
 //   q     = clamp(round(w / scale))  (f32 division, round half away from zero)
 // An all-zero block gets scale 0 and codes 0.
+#include <cstdlib>
 #include <cuda_fp8.h>
 
 #include "lq_internal.cuh"
@@ -490,101 +491,10 @@ void lq_launch_unpack(const lq_weight* w, int8_t* codes, float* scales, cudaStre
     LQ_CUDA(cudaGetLastError());
 }
 
-// Row-major bf16 dequantisation (int4 tiles or fp8 bytes -> out[m, k]) as a streaming kernel: the unit
-// of work is 16 bytes of output (8 elements = one packed int4 word, or 8 fp8 bytes); consecutive
-// lanes take consecutive units, so a warp reads 128 (256) contiguous bytes and writes whole 128-byte
-// lines, and each thread has kUnits independent loads in flight before its first store.  Values are
-// bf16(q * scale) resp. bf16(e4m3 * scale) from the f32 product, exactly as `dequant_tile_kernel`.
-constexpr int kDqUnits = 8;
-
-template <bool FP8>
-__global__ void __launch_bounds__(256) dequant_rows_kernel(LqWView w, __nv_bfloat16* __restrict__ out, int64_t ld,
-                                                           long long n_units) {
-    const long long base = (long long)blockIdx.x * (256 * kDqUnits) + threadIdx.x;
-    if (FP8) {
-        const long long upr = w.K >> 3;  // units per row (K % 16 == 0)
-        uint2 v[kDqUnits];
-        float sc[kDqUnits];
-#pragma unroll
-        for (int j = 0; j < kDqUnits; ++j) {
-            const long long u = base + j * 256;
-            v[j] = make_uint2(0u, 0u);
-            sc[j] = 0.f;
-            if (u < n_units) {
-                v[j] = __ldg((const uint2*)w.packed + u);
-                sc[j] = w.scale_kind == LQ_SCALE_PER_CHANNEL ? __ldg(w.scales + u / upr) : __ldg(w.scales);
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < kDqUnits; ++j) {
-            const long long u = base + j * 256;
-            if (u >= n_units) continue;
-            const long long m = u / upr, k = (u - m * upr) << 3;
-            const uint32_t words[2] = {v[j].x, v[j].y};
-            uint32_t o[4];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(words[h] & 0xFFFF), __NV_E4M3);
-                const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(words[h] >> 16), __NV_E4M3);
-                const float2 fl = __half22float2(*(const __half2*)&lo), fh = __half22float2(*(const __half2*)&hi);
-                o[h * 2] = pack_bf16x2(fl.x * sc[j], fl.y * sc[j]);
-                o[h * 2 + 1] = pack_bf16x2(fh.x * sc[j], fh.y * sc[j]);
-            }
-            *(uint4*)(out + m * ld + k) = make_uint4(o[0], o[1], o[2], o[3]);
-        }
-    } else {
-        // unit u = word u of the packed stream: tile u >> 10 = mt * k_tiles + kt, row (u >> 3) & 127, word u & 7
-        uint32_t v[kDqUnits];
-        float sc[kDqUnits];
-#pragma unroll
-        for (int j = 0; j < kDqUnits; ++j) {
-            const long long u = base + j * 256;
-            v[j] = 0u;
-            sc[j] = 0.f;
-            if (u < n_units) {
-                const long long tile = u >> 10, mt = tile / w.k_tiles, kt = tile - mt * w.k_tiles;
-                const int row = (int)(u >> 3) & 127, c = (int)u & 7;
-                v[j] = __ldg((const uint32_t*)w.packed + u);
-                if (kt * 64 + c * 8 < w.K)  // a column past K has no scale group
-                    sc[j] = __ldg(w.scales + (mt * w.n_groups + (kt * 64 + c * 8) / w.group) * 128 + row);
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < kDqUnits; ++j) {
-            const long long u = base + j * 256;
-            if (u >= n_units) continue;
-            const long long tile = u >> 10, mt = tile / w.k_tiles, kt = tile - mt * w.k_tiles;
-            const int row = (int)(u >> 3) & 127, c = (int)u & 7;
-            const long long m = mt * 128 + row, k = kt * 64 + c * 8;
-            if (m >= w.M || k >= w.K) continue;  // padding rows / columns of the last tiles
-            uint32_t o[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                // 2^23 + u as an f32 bit pattern, minus (2^23 + 8): the signed code, exactly
-                const float q0 = __uint_as_float(0x4B000000u | ((v[j] >> (4 * i)) & 0xFu)) - 8388616.f;
-                const float q1 = __uint_as_float(0x4B000000u | ((v[j] >> (4 * i + 16)) & 0xFu)) - 8388616.f;
-                o[i] = pack_bf16x2(q0 * sc[j], q1 * sc[j]);
-            }
-            *(uint4*)(out + m * ld + k) = make_uint4(o[0], o[1], o[2], o[3]);
-        }
-    }
-}
-
 void lq_launch_dequant(const lq_weight* w, void* out, int out_dtype, int64_t ld, int transpose, cudaStream_t st) {
     LqProf prof(LQ_K_DEQUANT, st);
     const bool aligned = (ld % 8 == 0) && (((uintptr_t)out & 15) == 0) && (w->M % 8 == 0) &&
                          (w->scheme != LQ_FP8_E4M3 || w->K % 16 == 0);
-    if (out_dtype == LQ_BF16 && aligned && !transpose && w->scheme != LQ_INT8) {
-        const bool fp8 = w->scheme == LQ_FP8_E4M3;
-        const long long n_units = fp8 ? (long long)w->M * (w->K / 8) : (long long)w->m_tiles * w->k_tiles * 1024;
-        const unsigned grid = (unsigned)((n_units + 256 * kDqUnits - 1) / (256 * kDqUnits));
-        if (fp8)
-            dequant_rows_kernel<true><<<grid, 256, 0, st>>>(lq_view(w), (__nv_bfloat16*)out, ld, n_units);
-        else
-            dequant_rows_kernel<false><<<grid, 256, 0, st>>>(lq_view(w), (__nv_bfloat16*)out, ld, n_units);
-        LQ_CUDA(cudaGetLastError());
-        return;
-    }
     if (out_dtype == LQ_BF16 && aligned) {
         dim3 grid((unsigned)((w->K + 63) / 64), (unsigned)((w->M + 127) / 128));
         dequant_tile_kernel<<<grid, 256, 0, st>>>(lq_view(w), (__nv_bfloat16*)out, ld, transpose);

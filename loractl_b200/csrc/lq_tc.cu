@@ -1037,12 +1037,22 @@ inline int pair_block_n(int64_t Mg, int64_t Ng, int sm_count, int kb_total = 0) 
     return cost(192) < cost(256) ? 192 : 256;
 }
 
+// Splits of a 64-wide contraction: the persistent grid walks `tiles * s` items in rounds of one CTA
+// per SM, so what counts is (rounds) x (k-blocks per item + a fixed cost per item), plus the partial
+// tiles the summing launch has to read.  (The former rule, about two items per SM, put config 2's
+// dH = dY . B^T at 5 splits = 320 items = 2.16 rounds run as 3; 4 splits run as 2.)
 int choose_splits(int64_t out_tiles, int64_t k_blocks, int sm_count) {
-    int64_t s = (2 * (int64_t)sm_count + out_tiles - 1) / out_tiles;
-    if (s > k_blocks) s = k_blocks;
-    if (s > 16) s = 16;
-    if (s < 1) s = 1;
-    return (int)s;
+    int best = 1;
+    double best_cost = 0.0;
+    for (int s = 1; s <= 16 && s <= k_blocks; ++s) {
+        const int64_t rounds = (out_tiles * s + sm_count - 1) / sm_count;
+        const double cost = (double)rounds * ((double)((k_blocks + s - 1) / s) + 4.0) + 0.75 * s;
+        if (s == 1 || cost < best_cost) {
+            best = s;
+            best_cost = cost;
+        }
+    }
+    return best;
 }
 
 inline size_t al256(size_t x) { return (x + 255) & ~size_t(255); }
@@ -1648,14 +1658,17 @@ void lq_tc_fwd(const lq_weight* w, const void* X, int64_t N, const float* A, con
     }
     ForkJoin fj(ctx, st, !((w4 || cached) && mirror));  // nothing is left for a second stream in that case
     fj.fork();
+    // main: H = X . A  (f32 [N, r] for the backward; bf16 s*H, zero padded, as the K extension).
+    // Enqueued BEFORE the side stream's dequantisation pass: that pass is thousands of small blocks
+    // which, launched first, hold every SM until they drain, so the two ran one after the other
+    // (config 2: 33 + 20 us); launched second they fill in beside the persistent 64-wide GEMM.
+    if (!mirror) cast_pad(A, 1, r, t.pdown, K, r, (int)K, (int)K, 1.f, st);  // A^T [r, K]
+    float* Hf = H_out ? H_out : t.Hf;
+    skinny_down(X, N, K, K, t.pdown, K, r, 1.f, Hf, t.ext_a, s, t.part, ctx.sm_count, st);
     // side: frozen weight -> bf16 scratch [M, K] (rounds q*scale, resp. LUT*scale, once to bf16),
     //       and B^T [M, EXT] for the K extension
     if (!w4 && !cached) lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, fj.side());
     if (!mirror) cast_pad(B, 1, M, t.pext, EXT, M, r, EXT, 1.f, fj.side());
-    // main: H = X . A  (f32 [N, r] for the backward; bf16 s*H, zero padded, as the K extension)
-    if (!mirror) cast_pad(A, 1, r, t.pdown, K, r, (int)K, (int)K, 1.f, st);  // A^T [r, K]
-    float* Hf = H_out ? H_out : t.Hf;
-    skinny_down(X, N, K, K, t.pdown, K, r, 1.f, Hf, t.ext_a, s, t.part, ctx.sm_count, st);
     fj.join(0);
     // Y = [X | s*H] . [W | B^T]^T + bias
     if (w4) {
@@ -1710,6 +1723,10 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
     }
     ForkJoin fj(ctx, st, true);
     fj.fork();
+    // main, first in issue order (see lq_tc_fwd): dH = s * dY . B^T   (f32 [N, r]; bf16 copy as the K
+    // extension of the dX GEMM and as dA's operand)
+    if (!mirror) cast_pad(B, M, 1, t.pdown, M, r, (int)M, (int)M, 1.f, st);  // B as bf16 [r, M]
+    skinny_down(dY, N, M, M, t.pdown, M, r, s, t.dHf, t.ext_a, 1.f, t.part, ctx.sm_count, st);
     // side: what the dX GEMM needs besides dH: W^T [K, M] and A [K, EXT] in bf16
     if (dX) {
         if (mn_scratch) lq_launch_dequant(w, t.wscr, LQ_BF16, K, 0, fj.side());       // W [M, K]
@@ -1728,9 +1745,6 @@ void lq_tc_bwd(const lq_weight* w, const void* dY, const void* X, const float* H
         }
         skinny_grad(dY, N, M, M, t.ext_b, r, 1.f, dB, 1, accumulate, t.part2, ctx.sm_count, fj.side());
     }
-    // main: dH = s * dY . B^T   (f32 [N, r]; bf16 copy as the K extension of the dX GEMM and as dA's operand)
-    if (!mirror) cast_pad(B, M, 1, t.pdown, M, r, (int)M, (int)M, 1.f, st);  // B as bf16 [r, M]
-    skinny_down(dY, N, M, M, t.pdown, M, r, s, t.dHf, t.ext_a, 1.f, t.part, ctx.sm_count, st);
     // dA[K, r] = X^T . dH needs dH only: with a dX GEMM to come it goes to the side stream behind the
     // dB chain, where its blocks fill the SMs the frozen GEMM's last, partly filled wave leaves idle
     // (its partials reuse `part`, which the dH reduction has finished with by then)
