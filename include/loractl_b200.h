@@ -304,6 +304,28 @@ int lq_gate_residual_bwd(const void* dout, const void* gate, const void* y, int 
                          int64_t tokens, int64_t h, void* dy, float* dgate, void* ws, size_t ws_bytes,
                          void* stream);
 
+/* The two activations between linears of the reference's own block, one pass forward and one pass
+ * backward each, over `n` contiguous elements of type `dtype` (LQ_F32 or LQ_BF16; f32 arithmetic;
+ * 16-byte aligned pointers):
+ *   SwiGLU (crates/loractl-core/src/mmdit.rs:695-708)            out = silu(gate) * up
+ *   attention output gate (crates/loractl-core/src/mmdit.rs:659-664)   out = x * sigmoid(gate)
+ * The reference runs each as two or three burn tensor ops (and as many autodiff nodes). */
+int lq_swiglu_fwd(const void* gate, const void* up, int dtype, int64_t n, void* out, void* stream);
+int lq_swiglu_bwd(const void* dout, const void* gate, const void* up, int dtype, int64_t n,
+                  void* dgate, void* dup, void* stream);
+int lq_sigmoid_gate_fwd(const void* x, const void* gate, int dtype, int64_t n, void* out, void* stream);
+int lq_sigmoid_gate_bwd(const void* dout, const void* x, const void* gate, int dtype, int64_t n,
+                        void* dx, void* dgate, void* stream);
+
+/* ZRmsNorm (crates/loractl-core/src/mmdit.rs:282-330): y = x / sqrt(mean(x^2) + eps) * (scale + 1)
+ * over rows of `h` contiguous elements (`dtype` LQ_F32 or LQ_BF16; `scale` f32 [h], frozen: the
+ * backward yields dx only); `rstd` f32 [rows] is written by the forward (may be NULL when no backward
+ * follows) and read by the backward. */
+int lq_zrmsnorm_fwd(const void* x, const float* scale, int dtype, int64_t rows, int64_t h, float eps,
+                    void* y, float* rstd, void* stream);
+int lq_zrmsnorm_bwd(const void* dy, const void* x, const float* scale, const float* rstd, int dtype,
+                    int64_t rows, int64_t h, void* dx, void* stream);
+
 /* ---- diagnostics -------------------------------------------------------------- */
 
 /* Device-side waits in the kernels are bounded; one that gives up records a code in a
@@ -337,14 +359,20 @@ int lq_profile_collect(double* ms_by_kind, uint64_t* launches_by_kind, int n_kin
 /* Run-time switches of the kernel selection, for A/B measurements and tests (the reference selects
  * code paths through `compute.*` config keys, crates/loractl-core/src/config.rs:704-760; these are
  * the equivalent knobs below the boundary).  Process-wide; initial values come from the environment
- * variables of the same meaning (LQ_W4, LQ_W4_EXACT).
- *   "w4"        1 (default): int4 weights at >= 128 tokens are dequantised inside the GEMM mainloop
- *               and no bf16 copy of the weight is written to HBM; 0: dequantise into the workspace.
+ * variables of the same meaning (LQ_W4, LQ_W4_EXACT, LQ_BWD_MN, LQ_TAIL_SPLIT).
+ *   "w4"        1: int4 weights at >= 128 tokens are dequantised inside the GEMM mainloop and no bf16
+ *               copy of the weight is written to HBM; 0 (default: it measured faster at every size
+ *               tried): dequantise into the workspace.
  *   "w4_exact"  how the in-mainloop conversion forms a bf16 weight from (q, scale):
  *               1: bf16(q * scale) with the f32 product, bit-identical to the workspace path;
  *               2: fma(q, s_hi, bf16(q * s_lo)) with the scale split into two bf16 terms — one
  *                  rounding of q * scale except within 2^-18 of a rounding boundary;
  *               0: bf16(q * bf16(scale)).
+ *   "bwd_mn"    1: the backward dequantises W in its own orientation and the dX GEMM reads that
+ *               scratch as an MN-major operand; 0 (default): transposed scratch, K-major operand.
+ *   "tail_split" 1 (default): a frozen GEMM with a long reduction whose last (or only) round of the
+ *               persistent grid is at most half full has those tiles cut along k (f32 partial tiles
+ *               in the workspace, summed in a fixed order by a second launch); 0: whole tiles only.
  * Unknown names are LQ_ERR_INVALID. */
 int lq_option_set(const char* name, int value);
 

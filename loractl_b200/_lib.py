@@ -79,6 +79,12 @@ SIGNATURES = {
     "lq_ln_modulate_fwd": (_I, [_P, _P, _P, _I, _I64, _I64, _I64, C.c_float, _P, _P, _P, _P]),
     "lq_ln_modulate_bwd": (_I, [_P, _P, _P, _P, _P, _I, _I64, _I64, _I64, _P, _P, _P, _P, C.c_size_t, _P]),
     "lq_gate_residual_fwd": (_I, [_P, _P, _P, _I, _I64, _I64, _I64, _P, _P]),
+    "lq_zrmsnorm_fwd": (_I, [_P, _P, _I, _I64, _I64, _F, _P, _P, _P]),
+    "lq_zrmsnorm_bwd": (_I, [_P, _P, _P, _P, _I, _I64, _I64, _P, _P]),
+    "lq_swiglu_fwd": (_I, [_P, _P, _I, _I64, _P, _P]),
+    "lq_swiglu_bwd": (_I, [_P, _P, _P, _I, _I64, _P, _P, _P]),
+    "lq_sigmoid_gate_fwd": (_I, [_P, _P, _I, _I64, _P, _P]),
+    "lq_sigmoid_gate_bwd": (_I, [_P, _P, _P, _I, _I64, _P, _P, _P]),
     "lq_gate_residual_bwd": (_I, [_P, _P, _P, _I, _I64, _I64, _I64, _P, _P, _P, C.c_size_t, _P]),
     "lq_check_device_status": (_I, [_P]),
     "lq_selftest_bounded_wait": (_I, [C.c_uint, _P]),

@@ -2,6 +2,9 @@
 
     modulated_layer_norm(x, shift, scale) = layer_norm(x) * (1 + scale) + shift
     gated_residual(x, gate, y)            = x + gate * y
+    swiglu(gate, up)                      = silu(gate) * up           (mmdit.rs:695-708)
+    sigmoid_gate(x, gate)                 = x * sigmoid(gate)         (mmdit.rs:659-664)
+    zrmsnorm(x, scale)                    = x / sqrt(mean(x^2) + 1e-5) * (scale + 1)   (mmdit.rs:282-330)
 
 the pattern of crates/loractl-core/src/mmdit.rs:857-869 (`(prescale + 1) * prenorm(x) + preshift`,
 `x + pregate * attn(..)`, ...).  `x`, `y` are `[b, tokens, h]`; `shift`, `scale`, `gate` are
@@ -123,3 +126,80 @@ def modulated_layer_norm(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tens
 def gated_residual(x: torch.Tensor, gate: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
     """`x + gate * y`, one kernel."""
     return _GatedResidual.apply(x, gate, y)
+
+
+class _PairAct(torch.autograd.Function):
+    """Element-wise map of two same-shaped tensors with both input gradients from one backward pass."""
+
+    @staticmethod
+    def forward(ctx, a, b, kind):
+        _require_cuda(a, "input")
+        if a.shape != b.shape or a.dtype != b.dtype:
+            raise ValueError(f"operands must agree in shape and dtype, got {list(a.shape)} {a.dtype} / {list(b.shape)} {b.dtype}")
+        ac, bc = a.contiguous(), b.contiguous()
+        out = torch.empty_like(ac)
+        fn = L.lib().lq_swiglu_fwd if kind == "swiglu" else L.lib().lq_sigmoid_gate_fwd
+        with torch.cuda.device(a.device):
+            L.check(fn(ac.data_ptr(), bc.data_ptr(), _dtype_code(ac), ac.numel(), out.data_ptr(), _stream_ptr(a.device)))
+        ctx.save_for_backward(ac, bc)
+        ctx.kind = kind
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        ac, bc = ctx.saved_tensors
+        dc = dout.to(ac.dtype).contiguous()
+        da, db = torch.empty_like(ac), torch.empty_like(bc)
+        fn = L.lib().lq_swiglu_bwd if ctx.kind == "swiglu" else L.lib().lq_sigmoid_gate_bwd
+        with torch.cuda.device(ac.device):
+            L.check(fn(dc.data_ptr(), ac.data_ptr(), bc.data_ptr(), _dtype_code(ac), ac.numel(), da.data_ptr(),
+                       db.data_ptr(), _stream_ptr(ac.device)))
+        return da, db, None
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """`silu(gate) * up`, one kernel each way."""
+    return _PairAct.apply(gate, up, "swiglu")
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """`x * sigmoid(gate)`, one kernel each way."""
+    return _PairAct.apply(x, gate, "sigmoid_gate")
+
+
+ZRMS_EPS = 1e-5  # crates/loractl-core/src/mmdit.rs:282-330
+
+
+class _ZRmsNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, scale):
+        _require_cuda(x, "x")
+        h = x.shape[-1]
+        if scale.numel() != h:
+            raise ValueError(f"scale must hold {h} values, got {list(scale.shape)}")
+        xc = x.contiguous()
+        sc = scale.detach().to(torch.float32).contiguous()
+        rows = xc.numel() // h
+        y = torch.empty_like(xc)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            L.check(L.lib().lq_zrmsnorm_fwd(xc.data_ptr(), sc.data_ptr(), _dtype_code(xc), rows, h, ZRMS_EPS, y.data_ptr(),
+                                            rstd.data_ptr(), _stream_ptr(x.device)))
+        ctx.save_for_backward(xc, sc, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, sc, rstd = ctx.saved_tensors
+        h = xc.shape[-1]
+        dc = dy.to(xc.dtype).contiguous()
+        dx = torch.empty_like(xc)
+        with torch.cuda.device(xc.device):
+            L.check(L.lib().lq_zrmsnorm_bwd(dc.data_ptr(), xc.data_ptr(), sc.data_ptr(), rstd.data_ptr(), _dtype_code(xc),
+                                            xc.numel() // h, h, dx.data_ptr(), _stream_ptr(xc.device)))
+        return dx, None
+
+
+def zrmsnorm(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """ZRmsNorm over the last axis with a frozen `scale` (no gradient flows to it), one kernel each way."""
+    return _ZRmsNorm.apply(x, scale)

@@ -10,6 +10,8 @@
 // the norm is a layer norm without affine parameters (eps inside the square root), statistics in
 // f32.  The token-axis sums of the backward (d shift, d scale, d gate) are written as per-chunk
 // partial rows and summed in a fixed order, so two runs are bit-identical.
+#include <algorithm>
+
 #include <cuda_bf16.h>
 
 #include "lq_internal.cuh"
@@ -370,6 +372,122 @@ int guarded_call(F&& f) {
     }
 }
 
+// ---- activations between two linears of the reference's own block ------------------------------
+// SwiGLU (crates/loractl-core/src/mmdit.rs:695-708): out = silu(gate) * up, and the attention output's
+// sigmoid gate (mmdit.rs:659-664): out = x * sigmoid(g).  Both are plain element-wise maps of two
+// tensors; one pass forward, one pass backward producing both input gradients; arithmetic in f32.
+// MODE 0: out = silu(a) * b        d a = dout * b * sig(a) (1 + a (1 - sig(a))),  d b = dout * silu(a)
+// MODE 1: out = a * sigmoid(b)     d a = dout * sig(b),                           d b = dout * a * sig(b) (1 - sig(b))
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
+
+template <int MODE>
+__device__ __forceinline__ float act_fwd(float a, float b) {
+    return MODE == 0 ? a * sigmoid_f(a) * b : a * sigmoid_f(b);
+}
+template <int MODE>
+__device__ __forceinline__ void act_bwd(float a, float b, float g, float& da, float& db) {
+    if (MODE == 0) {
+        const float sg = sigmoid_f(a);
+        da = g * b * sg * (1.f + a * (1.f - sg));
+        db = g * a * sg;
+    } else {
+        const float sg = sigmoid_f(b);
+        da = g * sg;
+        db = g * a * sg * (1.f - sg);
+    }
+}
+
+// VEC elements per thread and step: 8 bf16 or 4 f32 (16-byte accesses); `n` need not be a multiple.
+template <typename T, int MODE, bool BWD>
+__global__ void __launch_bounds__(256) pair_act_kernel(const T* __restrict__ a, const T* __restrict__ b,
+                                                       const T* __restrict__ dout, int64_t n, T* __restrict__ o0,
+                                                       T* __restrict__ o1) {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const int64_t nv = n / VEC;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint4 va = ((const uint4*)a)[i], vb = ((const uint4*)b)[i];
+        uint4 vg = make_uint4(0u, 0u, 0u, 0u);
+        if (BWD) vg = ((const uint4*)dout)[i];
+        const T* pa = (const T*)&va;
+        const T* pb = (const T*)&vb;
+        const T* pg = (const T*)&vg;
+        uint4 r0, r1;
+        T* q0 = (T*)&r0;
+        T* q1 = (T*)&r1;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            if (BWD) {
+                float da, db;
+                act_bwd<MODE>(to_f(pa[e]), to_f(pb[e]), to_f(pg[e]), da, db);
+                q0[e] = from_f<T>(da);
+                q1[e] = from_f<T>(db);
+            } else {
+                q0[e] = from_f<T>(act_fwd<MODE>(to_f(pa[e]), to_f(pb[e])));
+            }
+        }
+        ((uint4*)o0)[i] = r0;
+        if (BWD) ((uint4*)o1)[i] = r1;
+    }
+    // ragged end (fewer than VEC elements), by the first threads of the grid
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t i = nv * VEC + t;
+    if (i < n) {
+        if (BWD) {
+            float da, db;
+            act_bwd<MODE>(to_f(a[i]), to_f(b[i]), to_f(dout[i]), da, db);
+            o0[i] = from_f<T>(da);
+            o1[i] = from_f<T>(db);
+        } else {
+            o0[i] = from_f<T>(act_fwd<MODE>(to_f(a[i]), to_f(b[i])));
+        }
+    }
+}
+
+// ---- ZRmsNorm (crates/loractl-core/src/mmdit.rs:282-330) -------------------------------------------
+// y = x / sqrt(mean(x^2) + eps) * (scale + 1) over the last axis, zero-initialised frozen `scale`;
+// one warp per row, statistics in f32.  Backward for x only (the scale belongs to the frozen base):
+//   g = dy * (scale + 1),  dx = r * (g - x * r^2 * mean(g * x)),  r = rstd of the row.
+template <typename T>
+__global__ void __launch_bounds__(256) zrmsnorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ scale,
+                                                           int64_t rows, int h, float eps, T* __restrict__ y,
+                                                           float* __restrict__ rstd) {
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const T* xr = x + row * h;
+    float ss = 0.f;
+    for (int i = lane; i < h; i += 32) {
+        const float v = to_f(xr[i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float r = 1.f / sqrtf(ss / (float)h + eps);
+    if (lane == 0 && rstd) rstd[row] = r;
+    T* yr = y + row * h;
+    for (int i = lane; i < h; i += 32) yr[i] = from_f<T>(to_f(xr[i]) * r * (scale[i] + 1.f));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) zrmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                                           const float* __restrict__ scale,
+                                                           const float* __restrict__ rstd, int64_t rows, int h,
+                                                           T* __restrict__ dx) {
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const T* xr = x + row * h;
+    const T* gr = dy + row * h;
+    const float r = rstd[row];
+    float dot = 0.f;
+    for (int i = lane; i < h; i += 32) dot = fmaf(to_f(gr[i]) * (scale[i] + 1.f), to_f(xr[i]), dot);
+    dot = warp_sum(dot) / (float)h;
+    T* dr = dx + row * h;
+    for (int i = lane; i < h; i += 32) {
+        const float g = to_f(gr[i]) * (scale[i] + 1.f);
+        dr[i] = from_f<T>(r * (g - to_f(xr[i]) * r * r * dot));
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -507,6 +625,96 @@ int lq_gate_residual_bwd(const void* dout, const void* gate, const void* y, int 
                                                                      nullptr, tokens, (int)h, chunks, p0, nullptr);
         }
         col_final_kernel<<<(unsigned)((samples * h + 255) / 256), 256, 0, st>>>(p0, chunks, (int)h, samples, dgate);
+        LQ_CUDA(cudaGetLastError());
+    });
+}
+
+
+// ---- SwiGLU / sigmoid gate ---------------------------------------------------------------------
+
+static void pair_act_launch(int mode, bool bwd, const void* a, const void* b, const void* dout, int dtype, int64_t n,
+                            void* o0, void* o1, cudaStream_t st) {
+    LQ_CHECK_ARG(dtype == LQ_F32 || dtype == LQ_BF16, "dtype must be LQ_F32 or LQ_BF16");
+    LQ_CHECK_ARG(n >= 0, "element count must be >= 0");
+    if (n == 0) return;
+    LQ_CHECK_ARG(a && b && o0 && (!bwd || (dout && o1)), "NULL argument");
+    LQ_CHECK_ARG(aligned16(a) && aligned16(b) && aligned16(o0) && (!bwd || (aligned16(dout) && aligned16(o1))),
+                 "tensors must be 16-byte aligned");
+    int dev = 0;
+    LQ_CUDA(cudaGetDevice(&dev));
+    LqProf prof(LQ_K_PREP, st);
+    const int vec = dtype == LQ_F32 ? 4 : 8;
+    const unsigned grid = grid_for(std::max<int64_t>(n / vec, 1), 256, 148 * 16);
+#define LQ_PAIR_ACT(T, M, B)                                                                                      \
+    pair_act_kernel<T, M, B><<<grid, 256, 0, st>>>((const T*)a, (const T*)b, (const T*)dout, n, (T*)o0, (T*)o1)
+    if (dtype == LQ_F32) {
+        if (mode == 0 && !bwd) LQ_PAIR_ACT(float, 0, false);
+        else if (mode == 0) LQ_PAIR_ACT(float, 0, true);
+        else if (!bwd) LQ_PAIR_ACT(float, 1, false);
+        else LQ_PAIR_ACT(float, 1, true);
+    } else {
+        if (mode == 0 && !bwd) LQ_PAIR_ACT(__nv_bfloat16, 0, false);
+        else if (mode == 0) LQ_PAIR_ACT(__nv_bfloat16, 0, true);
+        else if (!bwd) LQ_PAIR_ACT(__nv_bfloat16, 1, false);
+        else LQ_PAIR_ACT(__nv_bfloat16, 1, true);
+    }
+#undef LQ_PAIR_ACT
+    LQ_CUDA(cudaGetLastError());
+}
+
+int lq_swiglu_fwd(const void* gate, const void* up, int dtype, int64_t n, void* out, void* stream) {
+    return guarded_call([&] { pair_act_launch(0, false, gate, up, nullptr, dtype, n, out, nullptr, (cudaStream_t)stream); });
+}
+int lq_swiglu_bwd(const void* dout, const void* gate, const void* up, int dtype, int64_t n, void* dgate, void* dup,
+                  void* stream) {
+    return guarded_call([&] { pair_act_launch(0, true, gate, up, dout, dtype, n, dgate, dup, (cudaStream_t)stream); });
+}
+int lq_sigmoid_gate_fwd(const void* x, const void* gate, int dtype, int64_t n, void* out, void* stream) {
+    return guarded_call([&] { pair_act_launch(1, false, x, gate, nullptr, dtype, n, out, nullptr, (cudaStream_t)stream); });
+}
+int lq_sigmoid_gate_bwd(const void* dout, const void* x, const void* gate, int dtype, int64_t n, void* dx, void* dgate,
+                        void* stream) {
+    return guarded_call([&] { pair_act_launch(1, true, x, gate, dout, dtype, n, dx, dgate, (cudaStream_t)stream); });
+}
+
+
+// ---- ZRmsNorm ------------------------------------------------------------------------------------
+
+int lq_zrmsnorm_fwd(const void* x, const float* scale, int dtype, int64_t rows, int64_t h, float eps, void* y,
+                    float* rstd, void* stream) {
+    return guarded_call([&] {
+        LQ_CHECK_ARG(dtype == LQ_F32 || dtype == LQ_BF16, "dtype must be LQ_F32 or LQ_BF16");
+        LQ_CHECK_ARG(rows >= 0 && h >= 1 && h <= (1 << 20), "rows must be >= 0 and h in [1, 2^20]");
+        if (rows == 0) return;
+        LQ_CHECK_ARG(x && scale && y, "NULL argument");
+        cudaStream_t st = (cudaStream_t)stream;
+        LqProf prof(LQ_K_PREP, st);
+        const unsigned grid = (unsigned)((rows + 7) / 8);
+        if (dtype == LQ_F32)
+            zrmsnorm_fwd_kernel<float><<<grid, 256, 0, st>>>((const float*)x, scale, rows, (int)h, eps, (float*)y, rstd);
+        else
+            zrmsnorm_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, scale, rows, (int)h, eps,
+                                                                     (__nv_bfloat16*)y, rstd);
+        LQ_CUDA(cudaGetLastError());
+    });
+}
+
+int lq_zrmsnorm_bwd(const void* dy, const void* x, const float* scale, const float* rstd, int dtype, int64_t rows,
+                    int64_t h, void* dx, void* stream) {
+    return guarded_call([&] {
+        LQ_CHECK_ARG(dtype == LQ_F32 || dtype == LQ_BF16, "dtype must be LQ_F32 or LQ_BF16");
+        LQ_CHECK_ARG(rows >= 0 && h >= 1 && h <= (1 << 20), "rows must be >= 0 and h in [1, 2^20]");
+        if (rows == 0) return;
+        LQ_CHECK_ARG(dy && x && scale && rstd && dx, "NULL argument");
+        cudaStream_t st = (cudaStream_t)stream;
+        LqProf prof(LQ_K_PREP, st);
+        const unsigned grid = (unsigned)((rows + 7) / 8);
+        if (dtype == LQ_F32)
+            zrmsnorm_bwd_kernel<float><<<grid, 256, 0, st>>>((const float*)dy, (const float*)x, scale, rstd, rows, (int)h,
+                                                             (float*)dx);
+        else
+            zrmsnorm_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, scale,
+                                                                     rstd, rows, (int)h, (__nv_bfloat16*)dx);
         LQ_CUDA(cudaGetLastError());
     });
 }

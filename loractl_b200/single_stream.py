@@ -61,6 +61,10 @@ class ZRmsNorm(nn.Module):
         self.scale = nn.Parameter(torch.zeros(dim), requires_grad=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and not self.scale.requires_grad:
+            from .block_ops import zrmsnorm
+
+            return zrmsnorm(x, self.scale)
         xf = x.float()
         var = xf.pow(2).mean(dim=-1, keepdim=True)
         return (xf / (var + 1e-5).sqrt() * (self.scale.float() + 1.0)).to(x.dtype)
@@ -96,6 +100,28 @@ def additive_mask(mask: torch.Tensor) -> torch.Tensor:
     return (1.0 - outer) * MASK_NEG
 
 
+def _fusable(a: torch.Tensor, b: torch.Tensor) -> bool:
+    return a.is_cuda and a.dtype == b.dtype and a.dtype in (torch.float32, torch.bfloat16)
+
+
+def _swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """`silu(gate) * up` (mmdit.rs:695-708): the fused kernel on the GPU, plain tensor ops elsewhere."""
+    if _fusable(gate, up):
+        from .block_ops import swiglu
+
+        return swiglu(gate, up)
+    return F.silu(gate) * up
+
+
+def _sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """`x * sigmoid(gate)` (mmdit.rs:659-664)."""
+    if _fusable(x, gate):
+        from .block_ops import sigmoid_gate
+
+        return sigmoid_gate(x, gate)
+    return x * torch.sigmoid(gate)
+
+
 def _plain(d_in: int, d_out: int) -> BaseLinear:
     return BaseLinear.plain(nn.Linear(d_in, d_out, bias=False))
 
@@ -128,7 +154,7 @@ class MmditAttention(nn.Module):
         k, v = expand(k), expand(v)
         ctx = F.scaled_dot_product_attention(q, k, v, attn_mask=None if mask4 is None else mask4.to(q.dtype))
         merged = ctx.transpose(1, 2).reshape(b, l, heads * hd)
-        return site(adapters, f"{prefix}.wo", self.wo, merged * torch.sigmoid(gate))
+        return site(adapters, f"{prefix}.wo", self.wo, _sigmoid_gate(merged, gate))
 
 
 class SwiGlu(nn.Module):
@@ -140,7 +166,7 @@ class SwiGlu(nn.Module):
         self.gate, self.up, self.down = _plain(features, inner), _plain(features, inner), _plain(inner, features)
 
     def forward(self, x, adapters: Optional[LoraAdapters], prefix: str) -> torch.Tensor:
-        gated = F.silu(site(adapters, f"{prefix}.gate", self.gate, x)) * site(adapters, f"{prefix}.up", self.up, x)
+        gated = _swiglu(site(adapters, f"{prefix}.gate", self.gate, x), site(adapters, f"{prefix}.up", self.up, x))
         return site(adapters, f"{prefix}.down", self.down, gated)
 
 

@@ -85,3 +85,61 @@ def test_bad_shapes_are_loud():
         gated_residual(x[0], torch.zeros(2, 1, 64, device="cuda"), x[0])
     with pytest.raises(RuntimeError, match="CUDA"):
         modulated_layer_norm(x.cpu(), torch.zeros(2, 1, 64), torch.zeros(2, 1, 64))
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 3), (2, 5, 96), (1, 4608, 512), (3, 129, 521), (8192 * 3)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kind", ["swiglu", "sigmoid_gate"])
+def test_swiglu_and_sigmoid_gate_match_torch(shape, dtype, kind):
+    """`silu(gate) * up` (crates/loractl-core/src/mmdit.rs:695-708) and `x * sigmoid(gate)`
+    (mmdit.rs:659-664) as one kernel each way, against the PyTorch f32 composition: values and both
+    input gradients; element counts that are not a multiple of the 16-byte vector."""
+    from loractl_b200 import block_ops
+
+    g = torch.Generator(device="cuda").manual_seed(3)
+    shape = shape if isinstance(shape, tuple) else (shape,)
+    a = (torch.randn(shape, generator=g, device="cuda") * 2).to(dtype)
+    b = (torch.randn(shape, generator=g, device="cuda") * 2).to(dtype)
+    dout = torch.randn(shape, generator=g, device="cuda").to(dtype)
+    xs = [a.clone().requires_grad_(True), b.clone().requires_grad_(True)]
+    out = getattr(block_ops, kind)(*xs)
+    out.backward(dout)
+    ref_in = [a.float().clone().requires_grad_(True), b.float().clone().requires_grad_(True)]
+    ref = F.silu(ref_in[0]) * ref_in[1] if kind == "swiglu" else ref_in[0] * torch.sigmoid(ref_in[1])
+    ref.backward(dout.float())
+    tol = 1e-5 if dtype == torch.float32 else 8e-3
+    assert out.shape == a.shape and out.dtype == dtype and rel(out, ref) <= tol
+    for ours, theirs in zip(xs, ref_in):
+        assert ours.grad.shape == ours.shape and rel(ours.grad, theirs.grad) <= tol
+
+
+def test_pair_activations_reject_mismatched_operands():
+    from loractl_b200.block_ops import swiglu
+
+    a = torch.zeros(4, 8, device="cuda")
+    with pytest.raises(ValueError):
+        swiglu(a, torch.zeros(4, 7, device="cuda"))
+    with pytest.raises(ValueError):
+        swiglu(a, torch.zeros(4, 8, device="cuda", dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 16), (2, 6, 33, 16), (3, 129, 96), (1, 4608, 3072), (2, 24, 300, 128)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_zrmsnorm_matches_torch(shape, dtype):
+    """ZRmsNorm (crates/loractl-core/src/mmdit.rs:282-330) over the last axis, with a non-zero frozen
+    scale, against the PyTorch f32 composition: values and the input gradient."""
+    from loractl_b200.block_ops import zrmsnorm
+
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = (torch.randn(shape, generator=g, device="cuda") * 1.5 + 0.2).to(dtype)
+    scale = torch.randn(shape[-1], generator=g, device="cuda") * 0.3
+    dout = torch.randn(shape, generator=g, device="cuda").to(dtype)
+    xs = x.clone().requires_grad_(True)
+    out = zrmsnorm(xs, scale)
+    out.backward(dout)
+    xr = x.float().clone().requires_grad_(True)
+    ref = xr / (xr.pow(2).mean(dim=-1, keepdim=True) + 1e-5).sqrt() * (scale + 1.0)
+    ref.backward(dout.float())
+    tol = 2e-5 if dtype == torch.float32 else 8e-3
+    assert out.shape == x.shape and out.dtype == dtype
+    assert rel(out, ref) <= tol and rel(xs.grad, xr.grad) <= tol
