@@ -536,9 +536,9 @@ def run_ours(args):
         s_cmp.wait_event(ev_up[i])
         s_cmp.wait_event(ev_down[i])  # this slot's gradient bucket has been downloaded
         bk = buckets[i]
-        y, h = Q.linear_fwd_raw(wq, xbuf[i], a, b, s, fp8_compute=fp8c)
+        y, h = Q.linear_fwd_raw(wq, xbuf[i], a, b, s, fp8_compute=fp8c, mirror=mirror)
         dx, _, _ = Q.linear_bwd_raw(wq, dybuf[i], xbuf[i], h, a, b, s, da_out=bk[: k * r].view(k, r),
-                                    db_out=bk[k * r:].view(r, m), fp8_compute=fp8c)
+                                    db_out=bk[k * r:].view(r, m), fp8_compute=fp8c, mirror=mirror)
         if world > 1:
             dist.all_reduce(bk)
         ev_cmp[i].record(s_cmp)
