@@ -1033,7 +1033,7 @@ def run_train_step(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     if args.model == "gpt2":
-        line = measure_gpt2_step(dev, world, rank, args.steps, args.warmup)
+        line = measure_gpt2_step(dev, world, rank, args.steps, args.warmup, graphs=not args.no_graph)
     else:
         line = measure_train_step(dev, world, rank, args.blocks, args.batch, args.rank, args.steps, args.warmup,
                                   weight_copies=args.weight_copies, graphs=not args.no_graph)
@@ -1043,7 +1043,8 @@ def run_train_step(args):
         dist.destroy_process_group()
 
 
-def measure_gpt2_step(dev, world: int, rank: int, steps: int, warmup: int, batch: int = 8, seq: int = 1024):
+def measure_gpt2_step(dev, world: int, rank: int, steps: int, warmup: int, batch: int = 8, seq: int = 1024,
+                      graphs: bool = True):
     """The text workload: GPT-2-small-shaped decoder (12 layers, 768, 12 heads, MLP 3072, vocabulary
     50257; crates/loractl-core/src/gpt2.rs:93-103), every per-block projection int4 block 64, LoRA rank 8
     on q/k/v/o, seeded uniform token ids, next-token cross-entropy, AdamW on the flat adapter bucket;
@@ -1084,14 +1085,25 @@ def measure_gpt2_step(dev, world: int, rank: int, steps: int, warmup: int, batch
     gd = torch.Generator(device=dev).manual_seed(100 + rank)
     ids = torch.randint(0, cfg.vocab_size, (hi - lo, seq), generator=gd, device=dev)
 
+    flat.refresh_mirrors()
+    graphed = None
+    if graphs:  # forward + loss + backward as one CUDA graph (ids are a fixed tensor here)
+        from loractl_b200.harness import GraphedLossStep
+
+        graphed = GraphedLossStep(lambda: G.next_token_loss(model(ids, adapters, dtype=torch.bfloat16), ids), dev)
+
     def one():
         flat.zero_grad()
-        loss = G.next_token_loss(model(ids, adapters, dtype=torch.bfloat16), ids)
-        loss.backward()
+        if graphed is not None:
+            loss = graphed.replay()
+        else:
+            loss = G.next_token_loss(model(ids, adapters, dtype=torch.bfloat16), ids)
+            loss.backward()
         flat.gather_autograd_grads()
         nonfinite_flag(flat.grads, flat.flag)
         scale = dp.sync_gradients(flat.grads, flat.flag)
         optim.step(1e-4, grad_scale=scale, skip_flag=flat.flag)
+        flat.refresh_mirrors()  # the factors changed: every bf16 operand mirror in one batched launch
         return loss
 
     losses = [float(one()) for _ in range(max(warmup, 3))]
@@ -1128,7 +1140,8 @@ def measure_gpt2_step(dev, world: int, rank: int, steps: int, warmup: int, batch
         "scaling": "strong", "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "gpt2-small-shaped decoder", "layers": cfg.n_layer, "hidden": e, "heads": cfg.n_head,
                    "mlp": inner, "vocab": cfg.vocab_size, "lora_rank": 8, "lora_sites": "q, k, v, o",
-                   "global_batch": global_batch, "seq_len": seq, "quant": "int4 block 64", "parallelism": f"dp{world}"},
+                   "global_batch": global_batch, "seq_len": seq, "quant": "int4 block 64", "parallelism": f"dp{world}",
+                   "cuda_graphs": "forward + loss + backward as one graph" if graphs else "none (eager launches)"},
         "model": {"step_flops": step_fl, "tflops": step_fl / (ms / steps * 1e-3) / 1e12,
                   "lora_params": sum(p.numel() for d in adapters.deltas for p in (d.lora_a, d.lora_b))},
         "tokens_per_s": tok * steps / (ms * 1e-3), "loss_first": losses[0], "loss_last": float(last),

@@ -131,3 +131,52 @@ def test_benchmark_width_stack_matches_an_f32_twin_in_the_bf16_band():
             ga, gb = p.grad.float().cpu().numpy().ravel(), p2.grad.float().cpu().numpy().ravel()
             cos = float(ga @ gb / (np.linalg.norm(ga) * np.linalg.norm(gb) + 1e-30))
             assert cos >= 0.99, cos
+
+
+@pytest.mark.gpu
+def test_graphed_loss_step_replays_the_eager_step():
+    """Forward + loss + backward of the text model captured as one CUDA graph (`GraphedLossStep`) over
+    a fixed ids tensor and a flat gradient bucket: replaying it after copying new ids in gives the
+    eager step's loss and adapter gradients (same kernels; the attention backward's atomic adds are
+    the only noise), for two different batches."""
+    import loractl_b200 as lb
+    from loractl_b200.harness import GraphedLossStep
+    from loractl_b200.optim import FlatAdapters
+
+    cfg = G.Gpt2Config(vocab_size=512, n_positions=128, n_embd=256, n_layer=2, n_head=4, n_inner=1024)
+    torch.manual_seed(3)
+    m = G.Gpt2(cfg, split_qkv=True).cuda()
+    with torch.no_grad():
+        for _, base in m.base_linears():
+            base.as_plain().weight.normal_(0, 0.02)
+        m.wte.weight.normal_(0, 0.02)
+        m.wpe.weight.normal_(0, 0.01)
+    assert m.into_quantized(4, block=64) == (12, 0)
+    m = m.to(torch.bfloat16)
+    lcfg = LoraConfig(rank=8, alpha=16.0, targets=[TargetSpec(r"attn\.(q|k|v|c_proj)$")])
+    ad = build_adapters(m.injectable_sites(), lcfg, torch.device("cuda"))
+    g = torch.Generator(device="cuda").manual_seed(9)
+    with torch.no_grad():
+        for d in ad.deltas:
+            d.lora_b.copy_(torch.randn(d.lora_b.shape, generator=g, device="cuda") * 0.02)
+    flat = FlatAdapters(ad, torch.device("cuda"))
+    flat.refresh_mirrors()
+    ids = torch.randint(0, cfg.vocab_size, (4, 128), generator=g, device="cuda")
+    fn = lambda: G.next_token_loss(m(ids, ad, dtype=torch.bfloat16), ids)
+    step = GraphedLossStep(fn, torch.device("cuda"))
+    for seed in (1, 2):
+        new_ids = torch.randint(0, cfg.vocab_size, (4, 128), generator=torch.Generator(device="cuda").manual_seed(seed),
+                                device="cuda")
+        ids.copy_(new_ids)
+        flat.zero_grad()
+        loss_e = fn()
+        loss_e.backward()
+        flat.gather_autograd_grads()
+        grads_e, le = flat.grads.clone(), float(loss_e)
+        flat.zero_grad()
+        lg = float(step.replay())
+        flat.gather_autograd_grads()
+        lb.check_device_status()
+        assert abs(lg - le) <= 1e-5 * abs(le), (lg, le)
+        assert float(grads_e.abs().max()) > 0
+        assert float((flat.grads - grads_e).abs().max()) <= 1e-4 * float(grads_e.abs().max())
