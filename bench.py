@@ -938,7 +938,7 @@ def mmdit_step_flops(cfg, lora_rank: int, n_blocks: int, global_batch: int) -> i
 
 
 def measure_train_step(dev, world: int, rank: int, n_blocks: int, batch: int, lora_rank: int, steps: int,
-                       warmup: int, weight_copies: str = "none", graphs: bool = True):
+                       warmup: int, weight_copies: str = "none", graphs: bool = True, reduce_every: int = 1):
     """Times `steps` training steps of the double-stream stack on this rank's shard of the global
     batch (max over ranks, CUDA events, barrier + synchronize on both sides).  Returns the result
     dict on every rank; the process group, if any, is the caller's."""
@@ -954,7 +954,7 @@ def measure_train_step(dev, world: int, rank: int, n_blocks: int, batch: int, lo
     lo, hi = lb.dp.shard_range(global_batch, rank, world)
     b = hi - lo
     stack = BlockStack(n_blocks, cfg, lora_rank, float(lora_rank), dev, seed=5, weight_copies=weight_copies)
-    trainer = Trainer(stack, lr=1e-4, graphs=graphs)
+    trainer = Trainer(stack, lr=1e-4, graphs=graphs, reduce_every=reduce_every)
     g = torch.Generator(device=dev).manual_seed(100 + rank)  # per-rank data, identical weights
     h = cfg.hidden
     x0 = torch.randn((b, cfg.img_tokens, h), generator=g, device=dev, dtype=torch.bfloat16)
@@ -998,6 +998,7 @@ def measure_train_step(dev, world: int, rank: int, n_blocks: int, batch: int, lo
                    "mlp": cfg.mlp, "lora_rank": lora_rank, "global_batch": global_batch,
                    "samples_per_gpu": b, "tokens_per_sample": tokens, "quant": "int4 block 64",
                    "grad_checkpointing": True, "parallelism": f"dp{world}",
+                   "grad_allreduce": f"one slice per {reduce_every} block(s), started from the reverse sweep",
                    "cuda_graphs": "one per block forward, one head, one per block replay + backward" if graphs
                    else "none (eager launches)",
                    "weight_copies": {"none": "none (every call dequantises into the workspace)",
@@ -1036,7 +1037,8 @@ def run_train_step(args):
         line = measure_gpt2_step(dev, world, rank, args.steps, args.warmup, graphs=not args.no_graph)
     else:
         line = measure_train_step(dev, world, rank, args.blocks, args.batch, args.rank, args.steps, args.warmup,
-                                  weight_copies=args.weight_copies, graphs=not args.no_graph)
+                                  weight_copies=args.weight_copies, graphs=not args.no_graph,
+                                  reduce_every=args.reduce_every)
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -1162,6 +1164,8 @@ def main():
     ap.add_argument("--weight-copies", nargs="?", const="resident", default="block", choices=["none", "resident", "block"],
                     help="--regime step: bf16 copies of the frozen weights. resident: of every weight, for the whole "
                          "run; block: two arenas of one block's copies, refilled one block ahead on a side stream")
+    ap.add_argument("--reduce-every", type=int, default=1,
+                    help="--regime step: blocks per gradient all-reduce of the reverse sweep (1 = per block)")
     ap.add_argument("--stream-tokens", default="1,8,16,64", help="--regime stream: token counts, comma separated")
     ap.add_argument("--stream-only", default=None, choices=["3072x3072", "3072x12288", "3072x12288-fp8"],
                     help="--regime stream: only this site shape (short runs for a profiler capture)")

@@ -204,7 +204,7 @@ int lq_linear_fwd(const lq_weight_t* w, const void* X, int64_t n_tokens, int dty
  * (NULL: recomputed as X . A); dA, dB are f32 and are OVERWRITTEN unless
  * `accumulate` is non-zero (then added to, for a flat gradient bucket).
  * dX may be NULL (input needs no gradient); dA/dB may be NULL when rank == 0.
- * Routes (bf16): int4 weights with quant block 64 at <= 16 tokens read the packed weight once and
+ * Routes (bf16): int4 weights at <= 16 tokens read the packed weight once and
  * convert it in registers (no bf16 image of W^T is written; dH, dA, dB are formed by the same two
  * launches); everything else dequantises into the workspace, or reads an attached bf16 copy. */
 int lq_linear_bwd(const lq_weight_t* w, const void* dY, const void* X, const float* H,

@@ -12,7 +12,7 @@
 //
 // Weight stream kernel, 160 threads, 3 CTAs per SM.  A work item is (chunk of 4 adjacent k-tiles,
 // split z of the m-tiles); a pipeline stage holds one m-tile of the chunk: the 4 packed tiles (one
-// bulk copy of 16 KB: tiles of one m-tile are adjacent in k), their 4 x 128 group scales, and the
+// bulk copy of 16 KB: tiles of one m-tile are adjacent in k), their 4 (or 8) x 128 group scales, and the
 // [16 tokens x 128 m] slice of dY as two 128-byte-swizzled tensor boxes (rows past N and columns
 // past d_out read as zero).  Consumer warp c owns k-tile c of the chunk = 64 output columns.
 //
@@ -27,8 +27,10 @@
 //   reduction slots 2t, 2t+1, 2t+8, 2t+9  <->  m = m0 + t, m0 + 4 + t, m0 + 8 + t, m0 + 12 + t
 // The group scale varies along the reduction (one per weight row), so it is folded into the token
 // operand instead: b'[m, n] = bf16(dY[n, m] * scale[m, tile]).  The +136 offset is removed with one
-// extra MMA against an all-ones row operand per 16 m (sum of b' per token).  Quant block 64 only (a
-// k-tile is then one scale group; block 32 sites take the tensor-regime path).
+// extra MMA against an all-ones row operand per 16 m (sum of b' per token).  With quant block 32 a
+// k-tile holds two scale groups (words 0-3 and 4-7 of a row) and an MMA must stay inside one: lanes g
+// and g + 4 then share word 4h + (g & 3) and split its elements by parity, two token operands and two
+// offset sums per 16 m (the reference's own block size, crates/loractl-core/src/quant.rs:52).
 //
 // The first CTAs of the grid compute partial rows of dH = s * dY . B^T (and of H = X . A when the
 // caller did not keep it) in f32; the finalize kernel sums the splits in a fixed order, adds the
@@ -81,7 +83,7 @@ constexpr int KC = 4;                      // k-tiles per chunk = consumer warps
 constexpr int NT = 16;                     // token rows of the dY boxes
 constexpr uint32_t DY_BYTES = 2 * NT * 128;  // two boxes [16 tokens][64 m] bf16
 constexpr uint32_t P_OFF = DY_BYTES, S_OFF = P_OFF + KC * 4096;
-constexpr uint32_t STAGE_BYTES = S_OFF + KC * 512;  // 22 KB, a multiple of 1024
+constexpr uint32_t STAGE_BYTES = S_OFF + KC * 1024;  // 24 KB (scales: up to two groups per k-tile), a multiple of 1024
 constexpr int STAGES = 2;  // three stages (a whole item in flight) measured no faster
 constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 128;
 constexpr int CTAS_PER_SM = 3;
@@ -160,7 +162,8 @@ __device__ __forceinline__ void row_partial(const __nv_bfloat16* __restrict__ x,
     }
 }
 
-template <int NB>
+// GPT = scale groups per 64-wide k-tile: 1 (quant block 64) or 2 (block 32).
+template <int NB, int GPT>
 __global__ void __launch_bounds__(kThreads, CTAS_PER_SM)
 stream_small_bwd_kernel(const __grid_constant__ CUtensorMap tmDY, const __grid_constant__ BwdParams p) {
     extern __shared__ uint8_t smem_raw_[];
@@ -215,13 +218,13 @@ stream_small_bwd_kernel(const __grid_constant__ CUtensorMap tmDY, const __grid_c
                     if (!mbar_wait(smem_u32(&empty[s]), phase ^ 1u, abort_flag, p.status, 35)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&full[s]);
                     const uint32_t base = smem_u32(raw + (size_t)s * STAGE_BYTES);
-                    mbar_expect_tx(bar, DY_BYTES + (uint32_t)tiles * (4096u + 512u));  // the dY boxes are always whole
+                    mbar_expect_tx(bar, DY_BYTES + (uint32_t)tiles * (4096u + GPT * 512u));  // the dY boxes are always whole
                     tma_load_2d(base, &tmDY, bar, mt * 128, 0);
                     tma_load_2d(base + NT * 128, &tmDY, bar, mt * 128 + 64, 0);
                     bulk_load(base + P_OFF, p.packed + ((size_t)mt * p.k_tiles + (size_t)kc * KC) * 4096,
                               (uint32_t)tiles * 4096u, bar);
-                    bulk_load(base + S_OFF, p.scales + ((size_t)mt * p.n_groups + (size_t)kc * KC) * 128,
-                              (uint32_t)tiles * 512u, bar);
+                    bulk_load(base + S_OFF, p.scales + ((size_t)mt * p.n_groups + (size_t)kc * KC * GPT) * 128,
+                              (uint32_t)tiles * GPT * 512u, bar);
                     if (++s == STAGES) { s = 0; phase ^= 1u; }
                 }
             }
@@ -242,12 +245,15 @@ stream_small_bwd_kernel(const __grid_constant__ CUtensorMap tmDY, const __grid_c
         const int mt0 = (int)(((long long)z * p.m_tiles) / p.splits);
         const int mt1 = (int)(((long long)(z + 1) * p.m_tiles) / p.splits);
         const bool live = kc * KC + cw < p.k_tiles;  // the last chunk may hold fewer than KC tiles
-        float acc[4][NB][4], one[NB][4];
+        // GPT 1: acc[j] = MMA j of the tile, one[0] its offset sums.  GPT 2: acc[2h + jj] = MMA jj of scale
+        // group h (k = 32h .. 32h + 31), one[h] that group's offset sums.
+        float acc[4][NB][4], one[GPT][NB][4];
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                one[nb][e] = 0.f;
+#pragma unroll
+                for (int h = 0; h < GPT; ++h) one[h][nb][e] = 0.f;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[j][nb][e] = 0.f;
             }
@@ -255,48 +261,81 @@ stream_small_bwd_kernel(const __grid_constant__ CUtensorMap tmDY, const __grid_c
             if (!mbar_wait(smem_u32(&full[s]), phase, abort_flag, p.status, 36)) { ok = false; break; }
             if (live) {
                 const uint8_t* stage = raw + (size_t)s * STAGE_BYTES;
-                const uint32_t* pk = (const uint32_t*)(stage + P_OFF + cw * 4096) + g;
-                const float* sc = (const float*)(stage + S_OFF) + cw * 128;
+                const uint32_t* pk = (const uint32_t*)(stage + P_OFF + cw * 4096);
+                const float* sc = (const float*)(stage + S_OFF) + cw * GPT * 128;
                 const int mrem = p.M - mt * 128;
 #pragma unroll 2
                 for (int c = 0; c < 8; ++c) {
                     const int m0 = c * 16 + t;  // this lane's four reduction rows: m0, m0 + 4, m0 + 8, m0 + 12
-                    const uint32_t wA = pk[m0 * 8], wB = pk[(m0 + 4) * 8], wC = pk[(m0 + 8) * 8], wD = pk[(m0 + 12) * 8];
-                    // rows past d_out (last m-tile): dY reads as zero there, and the scale must not turn it into NaN
-                    const float sA = m0 < mrem ? sc[m0] : 0.f, sB = m0 + 4 < mrem ? sc[m0 + 4] : 0.f;
-                    const float sC = m0 + 8 < mrem ? sc[m0 + 8] : 0.f, sD = m0 + 12 < mrem ? sc[m0 + 12] : 0.f;
-                    uint32_t b0[NB], b1[NB];
+                    float dy[NB][4];
 #pragma unroll
                     for (int nb = 0; nb < NB; ++nb) {
                         const int n = nb * 8 + g;
                         // [16 tokens][64 m] boxes, 128-byte swizzle: 16-byte chunk index ^ (token & 7)
                         const uint8_t* row = stage + (c >> 2) * (NT * 128) + n * 128;
                         const int ml = (c & 3) * 16 + t;  // m0 within its box; m0 + 4i stays inside the same 16
-                        auto at = [&](int mm) -> float {
-                            const uint32_t off = ((((uint32_t)mm >> 3) ^ ((uint32_t)n & 7u)) << 4) + (((uint32_t)mm & 7u) << 1);
-                            return __bfloat162float(*(const __nv_bfloat16*)(row + off));
-                        };
-                        b0[nb] = pack_bf16x2(at(ml) * sA, at(ml + 4) * sB);
-                        b1[nb] = pack_bf16x2(at(ml + 8) * sC, at(ml + 12) * sD);
-                    }
-                    const uint32_t eA = wA & 0x0F0F0F0Fu, oA = (wA >> 4) & 0x0F0F0F0Fu;
-                    const uint32_t eB = wB & 0x0F0F0F0Fu, oB = (wB >> 4) & 0x0F0F0F0Fu;
-                    const uint32_t eC = wC & 0x0F0F0F0Fu, oC = (wC >> 4) & 0x0F0F0F0Fu;
-                    const uint32_t eD = wD & 0x0F0F0F0Fu, oD = (wD >> 4) & 0x0F0F0F0Fu;
-                    // element e of a word sits in nibble (e >> 1) + 4 (e & 1): elements 0, 4, 1, 5 are bytes
-                    // 0..3 of the even-nibble word, elements 2, 6, 3, 7 those of the odd-nibble word
 #pragma unroll
-                    for (int nb = 0; nb < NB; ++nb) {
-                        // MMA j: fragment rows g / g + 8 = elements j / j + 4 of word g
-                        mma_16816(acc[0][nb], nib_pair(eA, eB, 0x0400u), nib_pair(eA, eB, 0x0501u), nib_pair(eC, eD, 0x0400u),
-                                  nib_pair(eC, eD, 0x0501u), b0[nb], b1[nb]);
-                        mma_16816(acc[1][nb], nib_pair(eA, eB, 0x0602u), nib_pair(eA, eB, 0x0703u), nib_pair(eC, eD, 0x0602u),
-                                  nib_pair(eC, eD, 0x0703u), b0[nb], b1[nb]);
-                        mma_16816(acc[2][nb], nib_pair(oA, oB, 0x0400u), nib_pair(oA, oB, 0x0501u), nib_pair(oC, oD, 0x0400u),
-                                  nib_pair(oC, oD, 0x0501u), b0[nb], b1[nb]);
-                        mma_16816(acc[3][nb], nib_pair(oA, oB, 0x0602u), nib_pair(oA, oB, 0x0703u), nib_pair(oC, oD, 0x0602u),
-                                  nib_pair(oC, oD, 0x0703u), b0[nb], b1[nb]);
-                        mma_16816(one[nb], ONES, ONES, ONES, ONES, b0[nb], b1[nb]);
+                        for (int i = 0; i < 4; ++i) {
+                            const uint32_t mm = (uint32_t)(ml + 4 * i);
+                            const uint32_t off = (((mm >> 3) ^ ((uint32_t)n & 7u)) << 4) + ((mm & 7u) << 1);
+                            dy[nb][i] = __bfloat162float(*(const __nv_bfloat16*)(row + off));
+                        }
+                    }
+                    // rows past d_out (last m-tile): dY reads as zero there, and the scale must not turn it into NaN
+                    const bool in0 = m0 < mrem, in1 = m0 + 4 < mrem, in2 = m0 + 8 < mrem, in3 = m0 + 12 < mrem;
+                    if constexpr (GPT == 1) {
+                        const uint32_t* pw = pk + g;  // word g of each row: 8 consecutive k
+                        const uint32_t wA = pw[m0 * 8], wB = pw[(m0 + 4) * 8], wC = pw[(m0 + 8) * 8], wD = pw[(m0 + 12) * 8];
+                        const float sA = in0 ? sc[m0] : 0.f, sB = in1 ? sc[m0 + 4] : 0.f;
+                        const float sC = in2 ? sc[m0 + 8] : 0.f, sD = in3 ? sc[m0 + 12] : 0.f;
+                        const uint32_t eA = wA & 0x0F0F0F0Fu, oA = (wA >> 4) & 0x0F0F0F0Fu;
+                        const uint32_t eB = wB & 0x0F0F0F0Fu, oB = (wB >> 4) & 0x0F0F0F0Fu;
+                        const uint32_t eC = wC & 0x0F0F0F0Fu, oC = (wC >> 4) & 0x0F0F0F0Fu;
+                        const uint32_t eD = wD & 0x0F0F0F0Fu, oD = (wD >> 4) & 0x0F0F0F0Fu;
+                        // element e of a word sits in nibble (e >> 1) + 4 (e & 1): elements 0, 4, 1, 5 are bytes
+                        // 0..3 of the even-nibble word, elements 2, 6, 3, 7 those of the odd-nibble word
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb) {
+                            const uint32_t b0 = pack_bf16x2(dy[nb][0] * sA, dy[nb][1] * sB);
+                            const uint32_t b1 = pack_bf16x2(dy[nb][2] * sC, dy[nb][3] * sD);
+                            // MMA j: fragment rows g / g + 8 = elements j / j + 4 of word g
+                            mma_16816(acc[0][nb], nib_pair(eA, eB, 0x0400u), nib_pair(eA, eB, 0x0501u),
+                                      nib_pair(eC, eD, 0x0400u), nib_pair(eC, eD, 0x0501u), b0, b1);
+                            mma_16816(acc[1][nb], nib_pair(eA, eB, 0x0602u), nib_pair(eA, eB, 0x0703u),
+                                      nib_pair(eC, eD, 0x0602u), nib_pair(eC, eD, 0x0703u), b0, b1);
+                            mma_16816(acc[2][nb], nib_pair(oA, oB, 0x0400u), nib_pair(oA, oB, 0x0501u),
+                                      nib_pair(oC, oD, 0x0400u), nib_pair(oC, oD, 0x0501u), b0, b1);
+                            mma_16816(acc[3][nb], nib_pair(oA, oB, 0x0602u), nib_pair(oA, oB, 0x0703u),
+                                      nib_pair(oC, oD, 0x0602u), nib_pair(oC, oD, 0x0703u), b0, b1);
+                            mma_16816(one[0][nb], ONES, ONES, ONES, ONES, b0, b1);
+                        }
+                    } else {
+                        // Two scale groups per tile (words 0-3, words 4-7): an MMA must stay inside one group,
+                        // so lanes g and g + 4 share word 4h + (g & 3) and take its elements of parity g >> 2:
+                        //   MMA (h, jj): fragment row g <-> element (g >> 2) + 2 jj, row g + 8 <-> that + 4
+                        const uint32_t sel0 = (g & 4) ? 0x0602u : 0x0400u, sel1 = (g & 4) ? 0x0703u : 0x0501u;
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const uint32_t* pw = pk + 4 * h + (g & 3);
+                            const uint32_t wA = pw[m0 * 8], wB = pw[(m0 + 4) * 8], wC = pw[(m0 + 8) * 8], wD = pw[(m0 + 12) * 8];
+                            const float* sh_ = sc + h * 128;
+                            const float sA = in0 ? sh_[m0] : 0.f, sB = in1 ? sh_[m0 + 4] : 0.f;
+                            const float sC = in2 ? sh_[m0 + 8] : 0.f, sD = in3 ? sh_[m0 + 12] : 0.f;
+                            const uint32_t eA = wA & 0x0F0F0F0Fu, oA = (wA >> 4) & 0x0F0F0F0Fu;
+                            const uint32_t eB = wB & 0x0F0F0F0Fu, oB = (wB >> 4) & 0x0F0F0F0Fu;
+                            const uint32_t eC = wC & 0x0F0F0F0Fu, oC = (wC >> 4) & 0x0F0F0F0Fu;
+                            const uint32_t eD = wD & 0x0F0F0F0Fu, oD = (wD >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+                            for (int nb = 0; nb < NB; ++nb) {
+                                const uint32_t b0 = pack_bf16x2(dy[nb][0] * sA, dy[nb][1] * sB);
+                                const uint32_t b1 = pack_bf16x2(dy[nb][2] * sC, dy[nb][3] * sD);
+                                mma_16816(acc[2 * h][nb], nib_pair(eA, eB, sel0), nib_pair(eA, eB, sel1),
+                                          nib_pair(eC, eD, sel0), nib_pair(eC, eD, sel1), b0, b1);
+                                mma_16816(acc[2 * h + 1][nb], nib_pair(oA, oB, sel0), nib_pair(oA, oB, sel1),
+                                          nib_pair(oC, oD, sel0), nib_pair(oC, oD, sel1), b0, b1);
+                                mma_16816(one[h][nb], ONES, ONES, ONES, ONES, b0, b1);
+                            }
+                        }
                     }
                 }
             }
@@ -306,25 +345,38 @@ stream_small_bwd_kernel(const __grid_constant__ CUtensorMap tmDY, const __grid_c
         }
         if (!ok) break;
         if (live) {
-            // fragment (row g, columns 2t / 2t+1) of MMA j = dX partial of k = 8g + j for tokens 2t, 2t + 1;
-            // row g + 8 the same for k = 8g + j + 4: eight consecutive k per lane and token
             float* pz = p.part + (size_t)z * p.N * p.K;
-            const int k0 = (kc * KC + cw) * 64 + g * 8;
+            const int kt0 = (kc * KC + cw) * 64;
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
                 for (int col = 0; col < 2; ++col) {
                     const int n = nb * 8 + 2 * t + col;
                     if (n >= p.N) continue;
-                    const float off = 136.f * one[nb][col];
-                    float4 lo, hi;
-                    lo.x = acc[0][nb][col] - off; lo.y = acc[1][nb][col] - off;
-                    lo.z = acc[2][nb][col] - off; lo.w = acc[3][nb][col] - off;
-                    hi.x = acc[0][nb][2 + col] - off; hi.y = acc[1][nb][2 + col] - off;
-                    hi.z = acc[2][nb][2 + col] - off; hi.w = acc[3][nb][2 + col] - off;
-                    float* dst = pz + (size_t)n * p.K + k0;
-                    *(float4*)dst = lo;
-                    *(float4*)(dst + 4) = hi;
+                    float* dst = pz + (size_t)n * p.K + kt0;
+                    if constexpr (GPT == 1) {
+                        // fragment (row g, columns 2t / 2t+1) of MMA j = dX partial of k = 8g + j for tokens 2t,
+                        // 2t + 1; row g + 8 the same for k = 8g + j + 4: eight consecutive k per lane and token
+                        const float off = 136.f * one[0][nb][col];
+                        float4 lo, hi;
+                        lo.x = acc[0][nb][col] - off; lo.y = acc[1][nb][col] - off;
+                        lo.z = acc[2][nb][col] - off; lo.w = acc[3][nb][col] - off;
+                        hi.x = acc[0][nb][2 + col] - off; hi.y = acc[1][nb][2 + col] - off;
+                        hi.z = acc[2][nb][2 + col] - off; hi.w = acc[3][nb][2 + col] - off;
+                        *(float4*)(dst + g * 8) = lo;
+                        *(float4*)(dst + g * 8 + 4) = hi;
+                    } else {
+                        // MMA (h, jj), row g: k = 32h + 8 (g & 3) + (g >> 2) + 2 jj; row g + 8: that + 4
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const float off = 136.f * one[h][nb][col];
+                            float* d = dst + 32 * h + 8 * (g & 3) + (g >> 2);
+                            d[0] = acc[2 * h][nb][col] - off;
+                            d[2] = acc[2 * h + 1][nb][col] - off;
+                            d[4] = acc[2 * h][nb][2 + col] - off;
+                            d[6] = acc[2 * h + 1][nb][2 + col] - off;
+                        }
+                    }
                 }
             }
         }
@@ -444,7 +496,7 @@ bool lq_small_bwd_supported(const lq_weight* w, int64_t n_tokens, int rank) {
         return e && e[0] == '1';
     }();
     if (off) return false;
-    return w->scheme == LQ_INT4 && w->group == 64 && n_tokens >= 1 && n_tokens <= NT && rank <= 64 && w->K % 64 == 0 &&
+    return w->scheme == LQ_INT4 && (w->group == 64 || w->group == 32) && n_tokens >= 1 && n_tokens <= NT && rank <= 64 && w->K % 64 == 0 &&
            w->M % 8 == 0 && w->device >= 0;
 }
 
@@ -493,7 +545,9 @@ void lq_small_bwd(const lq_weight* w, const void* dY, const void* X, const float
     const int grid = std::min(p.kchunks * p.splits, slots) + p.h_blocks;
     if (grid > 0) {
         CUtensorMap tmDY = lq_tc_make_map(dY, w->M, N, w->M, NT);
-        auto kern = N <= 8 ? stream_small_bwd_kernel<1> : stream_small_bwd_kernel<2>;
+        const bool g32 = w->group == 32;
+        auto kern = N <= 8 ? (g32 ? stream_small_bwd_kernel<1, 2> : stream_small_bwd_kernel<1, 1>)
+                           : (g32 ? stream_small_bwd_kernel<2, 2> : stream_small_bwd_kernel<2, 1>);
         LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
         LqProf prof(LQ_K_GEMM_MAIN, st);
         launch_pdl(kern, dim3(grid), dim3(kThreads), SMEM, st, tmDY, p);

@@ -346,9 +346,11 @@ class Trainer:
     """One rank of the data-parallel LoRA trainer over a `BlockStack`."""
 
     def __init__(self, stack: BlockStack, lr: float = 1e-4, weight_decay: float = 1e-4, group=None,
-                 grad_checkpointing: bool = True, graphs: bool = False):
+                 grad_checkpointing: bool = True, graphs: bool = False, reduce_every: int = 1):
         """`graphs`: run the checkpointed sweep as CUDA graphs (`GraphedSweep`), captured at the first
-        step of each batch shape."""
+        step of each batch shape.  `reduce_every`: blocks per gradient all-reduce of the reverse sweep
+        (1 = one slice per block, started as soon as that block's backward is enqueued; the number of
+        blocks = one all-reduce of the whole bucket after the sweep)."""
         self.stack, self.lr, self.group = stack, lr, group
         self.optim = AdamW(stack.flat, weight_decay=weight_decay)
         self.scaler = DynamicLossScale(initial=1.0)  # bf16/f32 gradients do not need the f16 head-room
@@ -356,6 +358,7 @@ class Trainer:
         if graphs and not grad_checkpointing:
             raise ValueError("graphs=True captures the block-checkpointed sweep: it needs grad_checkpointing")
         self.graphs = graphs
+        self.reduce_every = max(int(reduce_every), 1)
         self._sweeps = {}
         self.steps_done = 0
 
@@ -377,10 +380,15 @@ class Trainer:
         reducer = dp.BucketReducer(flat.grads, self.group)
         # a block's gradients are final once its replayed backward is enqueued: their all-reduce
         # starts there and overlaps the replay of the blocks below it
+        n_blocks = len(stack.blocks)
+
         def after_block(i: int) -> None:
             if reducer.world > 1:
                 flat.gather_autograd_grads(stack.block_slices[i])
-                reducer.reduce_slice(*stack.block_slices[i])
+                done = n_blocks - i  # blocks whose gradients are final, counted from the top
+                if done % self.reduce_every == 0 or i == 0:
+                    top = min(i + (done - 1) % self.reduce_every, n_blocks - 1)
+                    reducer.reduce_slice(stack.block_slices[i][0], stack.block_slices[top][1])
 
         torch.cuda.nvtx.range_push("lq.sweep")  # forward, head, reverse sweep (+ per-block all-reduce starts)
         if self.graphs:

@@ -1,4 +1,4 @@
-"""GPU parity of the small-batch backward (N <= 16 tokens, int4 block 64): dX over the packed weight
+"""GPU parity of the small-batch backward (N <= 16 tokens, int4, quant block 64 or 32): dX over the packed weight
 stream with the nibbles converted in registers, dH / dA / dB formed by the same two launches.
 
 Tolerance: the bf16 path's band — dX within 6e-3 of its peak against the f32 oracle on the same
@@ -23,14 +23,14 @@ def lb():
     return loractl_b200
 
 
-def case(n, k, m, r, seed=5):
+def case(n, k, m, r, seed=5, block=64):
     w = seeded((m, k), seed, 0.02)
     x = bf16_round(seeded((n, k), seed + 1))
     dy = bf16_round(seeded((n, m), seed + 4))
     a = seeded((k, r), seed + 2, 1.0 / np.sqrt(k)) if r else None
     b = seeded((r, m), seed + 3, 0.01) if r else None
-    wq = lb().quantize_linear_weight(dev(w), 4, 64)
-    dq = O.dequantize(*O.quantize(w, 64, 4), 64)
+    wq = lb().quantize_linear_weight(dev(w), 4, block)
+    dq = O.dequantize(*O.quantize(w, block, 4), block)
     return wq, dq, x, dy, a, b
 
 
@@ -43,13 +43,14 @@ SHAPES = [
 ]
 
 
+@pytest.mark.parametrize("block", [64, 32])
 @pytest.mark.parametrize("n", [1, 3, 8, 11, 16])
 @pytest.mark.parametrize("k,m", SHAPES)
 @pytest.mark.parametrize("r", [0, 4, 32])
-def test_small_batch_backward_matches_oracle(n, k, m, r):
+def test_small_batch_backward_matches_oracle(n, k, m, r, block):
     from loractl_b200 import quant as Q
 
-    wq, dq, x, dy, a, b = case(n, k, m, r)
+    wq, dq, x, dy, a, b = case(n, k, m, r, block=block)
     xd, dyd = dev(x, torch.bfloat16), dev(dy, torch.bfloat16)
     ad, bd = (dev(a), dev(b)) if r else (None, None)
     _, h = Q.linear_fwd_raw(wq, xd, ad, bd, 2.0)
