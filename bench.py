@@ -597,7 +597,10 @@ def run_ours(args):
                      "peak": sus_peak, "frac": sus_tf / sus_peak if sus_peak else None,
                      "sm_mhz_median": sampler.median_sm_mhz(t_sus0, t_sus1) if sampler else None}
         # config 5: the 24-block stack, global batch 8 sharded over the ranks, rank 32, recompute on
-        extras["model_step"] = measure_train_step(dev, world, rank, 24, 8, 32, steps=3, warmup=2, weight_copies="block")
+        # resident bf16 copies of the frozen weights (16 GB of the 180) and one gradient all-reduce after the
+        # sweep: the fastest of the combinations measured on 8 GPUs
+        extras["model_step"] = measure_train_step(dev, world, rank, 24, 8, 32, steps=3, warmup=2,
+                                                  weight_copies="resident", reduce_every=24)
     clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
 
     flops = step_flops(n, k, m, r)
@@ -1038,7 +1041,7 @@ def run_train_step(args):
     else:
         line = measure_train_step(dev, world, rank, args.blocks, args.batch, args.rank, args.steps, args.warmup,
                                   weight_copies=args.weight_copies, graphs=not args.no_graph,
-                                  reduce_every=args.reduce_every)
+                                  reduce_every=args.reduce_every if args.reduce_every > 0 else args.blocks)
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -1161,11 +1164,12 @@ def main():
                          "step: LoRA training steps/s of a double-stream MMDiT block stack; "
                          "load: streaming quantize-at-load of one block from a scaled-fp8 checkpoint")
     ap.add_argument("--model", default="mmdit", choices=["mmdit", "gpt2"], help="--regime step: which caller of the path")
-    ap.add_argument("--weight-copies", nargs="?", const="resident", default="block", choices=["none", "resident", "block"],
+    ap.add_argument("--weight-copies", nargs="?", const="resident", default="resident", choices=["none", "resident", "block"],
                     help="--regime step: bf16 copies of the frozen weights. resident: of every weight, for the whole "
                          "run; block: two arenas of one block's copies, refilled one block ahead on a side stream")
-    ap.add_argument("--reduce-every", type=int, default=1,
-                    help="--regime step: blocks per gradient all-reduce of the reverse sweep (1 = per block)")
+    ap.add_argument("--reduce-every", type=int, default=0,
+                    help="--regime step: blocks per gradient all-reduce of the reverse sweep (1 = per block; "
+                         "0 = all blocks: one all-reduce after the sweep)")
     ap.add_argument("--stream-tokens", default="1,8,16,64", help="--regime stream: token counts, comma separated")
     ap.add_argument("--stream-only", default=None, choices=["3072x3072", "3072x12288", "3072x12288-fp8"],
                     help="--regime stream: only this site shape (short runs for a profiler capture)")

@@ -373,6 +373,8 @@ int lq_profile_collect(double* ms_by_kind, uint64_t* launches_by_kind, int n_kin
  *   "tail_split" 1 (default): a frozen GEMM with a long reduction whose last (or only) round of the
  *               persistent grid is at most half full has those tiles cut along k (f32 partial tiles
  *               in the workspace, summed in a fixed order by a second launch); 0: whole tiles only.
+ *   "reserve_sms" n (default 0): SMs the persistent GEMM grids leave free, for a trainer whose
+ *               collectives run beside them (LQ_RESERVE_SMS).
  * Unknown names are LQ_ERR_INVALID. */
 int lq_option_set(const char* name, int value);
 

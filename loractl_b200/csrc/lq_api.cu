@@ -607,7 +607,7 @@ int lq_option_set(const char* name, int value) {
     return guarded([&] {
         LQ_CHECK_ARG(name != nullptr, "option name is NULL");
         if (!lq_w4_option_set(name, value) && !lq_tc_option_set(name, value))
-            throw LqError(LQ_ERR_INVALID, std::string("unknown option '") + name + "' (known: w4, w4_exact, bwd_mn, tail_split)");
+            throw LqError(LQ_ERR_INVALID, std::string("unknown option '") + name + "' (known: w4, w4_exact, bwd_mn, tail_split, reserve_sms)");
     });
 }
 

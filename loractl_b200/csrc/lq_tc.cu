@@ -841,6 +841,17 @@ struct EpiScales {
     int col_bcast = 0;
 };
 
+// "reserve_sms" (LQ_RESERVE_SMS): SMs the persistent grids leave free.  A persistent grid sized to the
+// whole machine with a static item walk has a cliff when another kernel (an NCCL collective of the
+// data-parallel trainer) holds a few SMs for its whole life: the CTAs that do not fit start only when
+// resident ones exit, i.e. after their entire walk.  Leaving as many SMs free as the collective takes
+// (NCCL_MAX_CTAS) costs reserve / 148 of peak throughput and removes the cliff.
+std::atomic<int> g_reserve_sms{[] {
+    const char* e = getenv("LQ_RESERVE_SMS");
+    return e ? atoi(e) : 0;
+}()};
+inline int usable_sms(int sm_count) { return std::max(2, sm_count - std::max(0, g_reserve_sms.load())); }
+
 template <int BLOCK_N, bool A_MN, bool B_MN, typename OutT, bool F8 = false>
 void launch_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand* a1, const Operand* b1, int64_t K1,
                  OutT* Cout, int64_t ldc, int64_t split_stride, int64_t Mg, int64_t Ng, int splits, const float* bias,
@@ -883,7 +894,7 @@ void launch_gemm(const Operand& a0, const Operand& b0, int64_t K0, const Operand
     CUtensorMap tC = tA0;
     if (p.tma_store) tC = make_store_map(Cout, Ng, Mg, ldc);
     long long items = (long long)p.m_tiles * p.n_tiles * splits;
-    int grid = (int)std::min<long long>(items, ctx.sm_count);
+    int grid = (int)std::min<long long>(items, usable_sms(ctx.sm_count));
     auto kern = umma_gemm_kernel<BLOCK_N, A_MN, B_MN, OutT, F8>;
     LQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
     LqProf prof(prof_kind, st);
@@ -970,7 +981,7 @@ void launch_gemm_pair(const Operand& a0, const Operand& b0, int64_t K0, const Op
             LQ_CUDA(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
             pairs_by_dev[dev] = std::max(1, std::min(n, ctx.sm_count / 2));
         }
-        pairs = pairs_by_dev[dev];
+        pairs = std::min(pairs_by_dev[dev], usable_sms(ctx.sm_count) / 2);
     }
     // A thin last round (at most half the pairs busy) is cut along k so that it fills the machine:
     // config 2's backward is 384 tiles on 74 pairs = 5.19 rounds, which ran as 6.
@@ -1541,6 +1552,7 @@ size_t lq_tc_mirror_bytes(int64_t K, int64_t M, int r) { return r > 0 ? carve_mi
 bool lq_tc_option_set(const char* name, int value) {
     if (std::strcmp(name, "bwd_mn") == 0) { g_bwd_mn = value; return true; }
     if (std::strcmp(name, "tail_split") == 0) { g_tail_split = value; return true; }
+    if (std::strcmp(name, "reserve_sms") == 0) { g_reserve_sms = value; return true; }
     return false;
 }
 

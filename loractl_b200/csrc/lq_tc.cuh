@@ -88,7 +88,7 @@ void lq_w8a8_bwd(const lq_weight* w, const void* dY, const void* X, const float*
 // A0[Mg, d_out] . W.  (a1, b1): optional bf16 K extension [Mg, K1] / [Ng, K1] (the LoRA product).
 bool lq_w4_supported(const lq_weight* w, int64_t Mg, int transposed);
 bool lq_w4_option_set(const char* name, int value);  // "w4", "w4_exact"; false: unknown name
-bool lq_tc_option_set(const char* name, int value);  // "bwd_mn", "tail_split"; false: unknown name
+bool lq_tc_option_set(const char* name, int value);  // "bwd_mn", "tail_split", "reserve_sms"; false: unknown name
 void lq_w4_gemm(const lq_weight* w, int transposed, const void* A0, int64_t lda, const void* a1, int64_t lda1,
                 const void* b1, int64_t ldb1, int64_t K1, void* Cout, int64_t ldc, int64_t Mg, const float* bias,
                 cudaStream_t st);
