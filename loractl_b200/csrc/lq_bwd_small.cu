@@ -45,38 +45,14 @@
 
 #include "lq_internal.cuh"
 #include "lq_prof.cuh"
+#include "lq_stream.cuh"
 #include "lq_tc.cuh"
 #include "lq_umma.cuh"
 
 namespace {
 
 using namespace umma;
-
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
-bool pdl_enabled() {
-    static const bool on = [] {
-        const char* e = getenv("LQ_NO_PDL");
-        return !(e && e[0] == '1');
-    }();
-    return on;
-}
-
-template <typename... KArgs, typename... Args>
-void launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    LQ_CUDA(cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...));
-}
+using namespace lqstream;
 
 constexpr int kThreads = 32 + 128;
 constexpr int KC = 4;                      // k-tiles per chunk = consumer warps
@@ -107,15 +83,6 @@ struct BwdParams {
     float* dHpart;            // [dh_chunks][N][r]   (unscaled)
     float* Hpart;             // [h_chunks][N][r]    (only when the caller passed no H)
 };
-
-__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                          uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-        "{%0, %1, %2, %3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 
 // (nibble of x, nibble of y) as the bf16 pair (128 + u_x, 128 + u_y): `sel` picks one byte of each masked word
 __device__ __forceinline__ uint32_t nib_pair(uint32_t x, uint32_t y, uint32_t sel) {
