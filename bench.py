@@ -600,7 +600,7 @@ def run_ours(args):
         # resident bf16 copies of the frozen weights (16 GB of the 180) and one gradient all-reduce after the
         # sweep: the fastest of the combinations measured on 8 GPUs
         extras["model_step"] = measure_train_step(dev, world, rank, 24, 8, 32, steps=3, warmup=2,
-                                                  weight_copies="resident", reduce_every=24)
+                                                  weight_copies="resident", reduce_every=24, two_streams=True)
     clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
 
     flops = step_flops(n, k, m, r)
@@ -941,7 +941,8 @@ def mmdit_step_flops(cfg, lora_rank: int, n_blocks: int, global_batch: int) -> i
 
 
 def measure_train_step(dev, world: int, rank: int, n_blocks: int, batch: int, lora_rank: int, steps: int,
-                       warmup: int, weight_copies: str = "none", graphs: bool = True, reduce_every: int = 1):
+                       warmup: int, weight_copies: str = "none", graphs: bool = True, reduce_every: int = 1,
+                       two_streams: bool = False):
     """Times `steps` training steps of the double-stream stack on this rank's shard of the global
     batch (max over ranks, CUDA events, barrier + synchronize on both sides).  Returns the result
     dict on every rank; the process group, if any, is the caller's."""
@@ -956,7 +957,8 @@ def measure_train_step(dev, world: int, rank: int, n_blocks: int, batch: int, lo
     global_batch = max(batch, world)
     lo, hi = lb.dp.shard_range(global_batch, rank, world)
     b = hi - lo
-    stack = BlockStack(n_blocks, cfg, lora_rank, float(lora_rank), dev, seed=5, weight_copies=weight_copies)
+    stack = BlockStack(n_blocks, cfg, lora_rank, float(lora_rank), dev, seed=5, weight_copies=weight_copies,
+                       two_cuda_streams=two_streams)
     trainer = Trainer(stack, lr=1e-4, graphs=graphs, reduce_every=reduce_every)
     g = torch.Generator(device=dev).manual_seed(100 + rank)  # per-rank data, identical weights
     h = cfg.hidden
@@ -1001,6 +1003,7 @@ def measure_train_step(dev, world: int, rank: int, n_blocks: int, batch: int, lo
                    "mlp": cfg.mlp, "lora_rank": lora_rank, "global_batch": global_batch,
                    "samples_per_gpu": b, "tokens_per_sample": tokens, "quant": "int4 block 64",
                    "grad_checkpointing": True, "parallelism": f"dp{world}",
+                   "cuda_streams": "text chain beside the image chain (2 streams per block)" if two_streams else "one",
                    "grad_allreduce": f"one slice per {reduce_every} block(s), started from the reverse sweep",
                    "cuda_graphs": "one per block forward, one head, one per block replay + backward" if graphs
                    else "none (eager launches)",
@@ -1041,7 +1044,8 @@ def run_train_step(args):
     else:
         line = measure_train_step(dev, world, rank, args.blocks, args.batch, args.rank, args.steps, args.warmup,
                                   weight_copies=args.weight_copies, graphs=not args.no_graph,
-                                  reduce_every=args.reduce_every if args.reduce_every > 0 else args.blocks)
+                                  reduce_every=args.reduce_every if args.reduce_every > 0 else args.blocks,
+                                  two_streams=not args.one_stream)
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -1167,6 +1171,9 @@ def main():
     ap.add_argument("--weight-copies", nargs="?", const="resident", default="resident", choices=["none", "resident", "block"],
                     help="--regime step: bf16 copies of the frozen weights. resident: of every weight, for the whole "
                          "run; block: two arenas of one block's copies, refilled one block ahead on a side stream")
+    ap.add_argument("--one-stream", action="store_true",
+                    help="--regime step: a block's text and image chains one after the other on one CUDA stream "
+                         "(default: the text chain on a second stream beside the image chain)")
     ap.add_argument("--reduce-every", type=int, default=0,
                     help="--regime step: blocks per gradient all-reduce of the reverse sweep (1 = per block; "
                          "0 = all blocks: one all-reduce after the sweep)")

@@ -60,6 +60,7 @@ class DoubleStreamBlock(nn.Module):
 
     STREAMS = ("img", "txt")
     LINEARS = ("mod", "qkv", "out", "up", "down")
+    _SIDE_STREAMS: dict = {}
 
     def __init__(self, index: int, cfg: BlockConfig, gen: torch.Generator, device):
         super().__init__()
@@ -70,6 +71,7 @@ class DoubleStreamBlock(nn.Module):
                                     for s in self.STREAMS for n in self.LINEARS})
         self.adapters: Optional[LoraAdapters] = None
         self.cond: Optional[torch.Tensor] = None  # [b, hidden] conditioning, set per step
+        self.two_cuda_streams = False
 
     def sites(self) -> List[LoraSite]:
         return [LoraSite(self.path(s, n), self.bases[f"{s}_{n}"].d_in, self.bases[f"{s}_{n}"].d_out)
@@ -81,39 +83,61 @@ class DoubleStreamBlock(nn.Module):
     def _lin(self, stream: str, name: str, x: torch.Tensor) -> torch.Tensor:
         return site(self.adapters, self.path(stream, name), self.bases[f"{stream}_{name}"], x)
 
+    def _on_two_streams(self, fn) -> dict:
+        """`fn(s)` for both token streams.  With `two_cuda_streams` the text stream's chain runs on a second
+        CUDA stream beside the image stream's (forked from and joined back into the current stream, so
+        a stream capture records two parallel branches): its short kernels — 512 tokens per sample
+        against 4096 — fill the gaps of the long ones instead of queueing behind them."""
+        if not self.two_cuda_streams:
+            return {s: fn(s) for s in self.STREAMS}
+        cur = torch.cuda.current_stream()
+        key = (cur.device.index, cur.cuda_stream)  # one second stream per (device, calling stream), shared by all blocks
+        side = self._SIDE_STREAMS.get(key)
+        if side is None:
+            side = self._SIDE_STREAMS[key] = torch.cuda.Stream(device=cur.device)
+        side.wait_stream(cur)
+        out = {}
+        with torch.cuda.stream(side):
+            out["txt"] = fn("txt")
+        out["img"] = fn("img")
+        cur.wait_stream(side)
+        return out
+
     def forward(self, state: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
         b, _, h = state.shape
         li = cfg.img_tokens
         xs = {"img": state[:, :li], "txt": state[:, li:]}
         cond = F.silu(self.cond.to(state.dtype))
-        mods, qkvs = {}, {}
         # both streams' modulation projections read the same conditioning vector: one grouped call
         mod_out = site_group(self.adapters, [(self.path(s, "mod"), self.bases[f"{s}_mod"]) for s in self.STREAMS], cond)
-        for s, mo in zip(self.STREAMS, mod_out):
-            mods[s] = mo.unsqueeze(1).chunk(6, dim=-1)
-            shift, scale = mods[s][0], mods[s][1]
-            xn = modulated_layer_norm(xs[s], shift, scale)  # LN(x) * (1 + scale) + shift, one kernel
-            qkvs[s] = self._lin(s, "qkv", xn).view(b, -1, 3, cfg.heads, h // cfg.heads)
+        mods = {s: mo.unsqueeze(1).chunk(6, dim=-1) for s, mo in zip(self.STREAMS, mod_out)}
+
+        def to_qkv(s):
+            xn = modulated_layer_norm(xs[s], mods[s][0], mods[s][1])  # LN(x) * (1 + scale) + shift, one kernel
+            return self._lin(s, "qkv", xn).view(b, -1, 3, cfg.heads, h // cfg.heads)
+
+        qkvs = self._on_two_streams(to_qkv)
         qkv = torch.cat([qkvs["img"], qkvs["txt"]], dim=1)  # joint attention over both streams
         q, k, v = (t.transpose(1, 2) for t in qkv.unbind(2))
         att = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(b, -1, h)
         atts = {"img": att[:, :li], "txt": att[:, li:]}
-        outs = []
-        for s in self.STREAMS:
+
+        def after_attention(s):
             _, _, gate1, shift2, scale2, gate2 = mods[s]
             x = gated_residual(xs[s], gate1, self._lin(s, "out", atts[s]))
             xn = modulated_layer_norm(x, shift2, scale2)
-            x = gated_residual(x, gate2, self._lin(s, "down", F.gelu(self._lin(s, "up", xn), approximate="tanh")))
-            outs.append(x)
-        return torch.cat(outs, dim=1)
+            return gated_residual(x, gate2, self._lin(s, "down", F.gelu(self._lin(s, "up", xn), approximate="tanh")))
+
+        outs = self._on_two_streams(after_attention)
+        return torch.cat([outs[s] for s in self.STREAMS], dim=1)
 
 
 class BlockStack(nn.Module):
     """`n_blocks` double-stream blocks with one LoRA adapter set over every linear."""
 
     def __init__(self, n_blocks: int, cfg: BlockConfig, rank: int, alpha: float, device, seed: int = 5,
-                 dtype: torch.dtype = torch.bfloat16, weight_copies="none"):
+                 dtype: torch.dtype = torch.bfloat16, weight_copies="none", two_cuda_streams: bool = False):
         """`weight_copies`: "none" — every call dequantises into its workspace; "resident" (or True) —
         keep a bf16 copy of every frozen weight (2 bytes per element beside the packed 0.5), so that no
         call dequantises: the memory-for-time trade a 180 GB GPU allows; "block" — two arenas of one
@@ -138,6 +162,7 @@ class BlockStack(nn.Module):
                 d.lora_b.copy_(torch.randn(d.lora_b.shape, generator=g2, device=device) * 0.01)
         for blk in self.blocks:
             blk.adapters = self.adapters
+            blk.two_cuda_streams = bool(two_cuda_streams)  # text and image chains of a block on two CUDA streams
             if weight_copies == "resident":
                 for w in self._copy_weights(blk):
                     w.attach_bf16_copy()

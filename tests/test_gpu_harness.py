@@ -148,3 +148,30 @@ def test_graphed_sweep_trains_like_the_eager_sweep():
     # the block-ahead refill inside the graphs leaves exactly what the resident copies hold
     assert out[(True, "block")][0] == out[(True, "resident")][0]
     assert float((out[(True, "block")][1] - out[(True, "resident")][1]).abs().max()) <= 1e-4 * float(g0.abs().max())
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_text_and_image_chains_on_two_cuda_streams_change_nothing(graphs):
+    """A block's text chain on a second CUDA stream beside the image chain (`two_cuda_streams`) is a
+    scheduling change only: three training steps give the single-stream run's losses, gradients and
+    parameters (up to the attention backward's atomic-add noise), eagerly and from CUDA graphs, and
+    repeating the two-stream run reproduces itself to the same noise."""
+    from loractl_b200.harness import BlockConfig, BlockStack, Trainer
+
+    cfg = BlockConfig(hidden=256, heads=4, mlp=512, img_tokens=256, txt_tokens=128, quant_bits=4, quant_block=64)
+    runs = []
+    for two in (False, True, True):
+        stack = BlockStack(3, cfg, rank=4, alpha=8.0, device=torch.device("cuda"), seed=5, two_cuda_streams=two)
+        tr = Trainer(stack, lr=1e-3, weight_decay=0.0, graphs=graphs)
+        losses = [tr.step(*batch(cfg, b=2, seed=i)) for i in range(3)]
+        torch.cuda.synchronize()
+        runs.append((losses, stack.flat.grads.clone(), stack.flat.params.clone()))
+    import loractl_b200
+
+    loractl_b200.check_device_status()
+    (l0, g0, p0) = runs[0]
+    for l1, g1, p1 in runs[1:]:
+        assert all(abs(a - b) <= 1e-5 * abs(a) for a, b in zip(l0, l1)), (l0, l1)
+        assert torch.isfinite(g1).all()
+        assert float((g0 - g1).abs().max()) <= 1e-4 * float(g0.abs().max())
+        assert float((p0 - p1).abs().max()) <= 1e-5
