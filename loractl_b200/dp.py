@@ -62,6 +62,18 @@ class BucketReducer:
         return 1.0 / self.world
 
 
+def sweep_reduce_range(n_blocks: int, reduce_every: int, i: int):
+    """Blocks whose gradients are all-reduced right after block `i`'s backward in a reverse sweep
+    (`i` runs from `n_blocks - 1` down to 0) when one all-reduce covers `reduce_every` blocks: `(lo, hi)`
+    inclusive, or None when nothing is due yet.  Every block is covered exactly once; the last range
+    (at `i == 0`) may be shorter."""
+    reduce_every = max(int(reduce_every), 1)
+    done = n_blocks - i  # blocks whose gradients are final, counted from the top
+    if done % reduce_every != 0 and i != 0:
+        return None
+    return i, min(i + (done - 1) % reduce_every, n_blocks - 1)
+
+
 def reduce_flag(flag: torch.Tensor, group=None) -> None:
     """Max-allreduce of the 1-element non-finite flag, so that every rank takes the same decision."""
     if world_size(group) > 1:

@@ -410,10 +410,9 @@ class Trainer:
         def after_block(i: int) -> None:
             if reducer.world > 1:
                 flat.gather_autograd_grads(stack.block_slices[i])
-                done = n_blocks - i  # blocks whose gradients are final, counted from the top
-                if done % self.reduce_every == 0 or i == 0:
-                    top = min(i + (done - 1) % self.reduce_every, n_blocks - 1)
-                    reducer.reduce_slice(stack.block_slices[i][0], stack.block_slices[top][1])
+                due = dp.sweep_reduce_range(n_blocks, self.reduce_every, i)
+                if due is not None:
+                    reducer.reduce_slice(stack.block_slices[due[0]][0], stack.block_slices[due[1]][1])
 
         torch.cuda.nvtx.range_push("lq.sweep")  # forward, head, reverse sweep (+ per-block all-reduce starts)
         if self.graphs:

@@ -140,3 +140,24 @@ def test_two_rank_per_block_buckets_equal_one_flat_allreduce():
     red = dp.BucketReducer(torch.ones(4))
     red.reduce_slice(0, 4)
     assert red.finish() == 1.0
+
+
+def test_sweep_reduce_ranges_cover_every_block_once():
+    """Blocks per gradient all-reduce of the reverse sweep: whatever the grouping, every block's slice is
+    reduced exactly once, each range is due only when its lowest block's backward has been enqueued,
+    and grouping all blocks gives the single all-reduce after the sweep."""
+    from loractl_b200.dp import sweep_reduce_range
+
+    for n_blocks in (1, 2, 5, 24):
+        for every in (1, 2, 4, 5, 24, 100):
+            seen = []
+            for i in range(n_blocks - 1, -1, -1):
+                due = sweep_reduce_range(n_blocks, every, i)
+                if due is not None:
+                    lo, hi = due
+                    assert lo == i and lo <= hi < n_blocks and hi - lo + 1 <= every
+                    seen += list(range(lo, hi + 1))
+            assert sorted(seen) == list(range(n_blocks)), (n_blocks, every, seen)
+    assert sweep_reduce_range(24, 24, 0) == (0, 23)
+    assert all(sweep_reduce_range(24, 24, i) is None for i in range(1, 24))
+    assert sweep_reduce_range(24, 1, 7) == (7, 7)
