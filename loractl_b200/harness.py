@@ -54,6 +54,27 @@ def _quant_site(d_in: int, d_out: int, cfg: BlockConfig, gen: torch.Generator, d
     return BaseLinear.quant(QuantLinear(quantize_linear_weight(w, cfg.quant_bits, cfg.quant_block)))
 
 
+class _SplitStreams(torch.autograd.Function):
+    """`[b, img + txt, h]` -> contiguous `[b, img, h]`, `[b, txt, h]`, once per tensor: with b > 1 the
+    plain slices are non-contiguous and every fused op behind them made its own strided copy, every
+    slice backward its own zero-filled full-size gradient.  The backward is one concatenation."""
+
+    @staticmethod
+    def forward(ctx, x, li):
+        return x[:, :li].contiguous(), x[:, li:].contiguous()
+
+    @staticmethod
+    def backward(ctx, g_img, g_txt):
+        return torch.cat([g_img, g_txt], dim=1), None
+
+
+def split_streams(x: torch.Tensor, li: int):
+    """(image part, text part) of `[b, img + txt, h]` along the token axis, each contiguous."""
+    if x.shape[0] == 1:  # the slices of a single sample are contiguous views already
+        return x[:, :li], x[:, li:]
+    return _SplitStreams.apply(x, li)
+
+
 class DoubleStreamBlock(nn.Module):
     """One double-stream block; the block state is the concatenation [img tokens | txt tokens]
     along the sequence axis so that block-checkpointing sees a single tensor."""
@@ -107,7 +128,7 @@ class DoubleStreamBlock(nn.Module):
         cfg = self.cfg
         b, _, h = state.shape
         li = cfg.img_tokens
-        xs = {"img": state[:, :li], "txt": state[:, li:]}
+        xs = dict(zip(self.STREAMS, split_streams(state, li)))
         cond = F.silu(self.cond.to(state.dtype))
         # both streams' modulation projections read the same conditioning vector: one grouped call
         mod_out = site_group(self.adapters, [(self.path(s, "mod"), self.bases[f"{s}_mod"]) for s in self.STREAMS], cond)
@@ -121,7 +142,7 @@ class DoubleStreamBlock(nn.Module):
         qkv = torch.cat([qkvs["img"], qkvs["txt"]], dim=1)  # joint attention over both streams
         q, k, v = (t.transpose(1, 2) for t in qkv.unbind(2))
         att = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(b, -1, h)
-        atts = {"img": att[:, :li], "txt": att[:, li:]}
+        atts = dict(zip(self.STREAMS, split_streams(att, li)))
 
         def after_attention(s):
             _, _, gate1, shift2, scale2, gate2 = mods[s]
