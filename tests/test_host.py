@@ -111,3 +111,23 @@ def test_host_fp8_lut_and_scale_kinds(golden_dir):
     assert scale_kind_for((5, 3), (5,)) == L.LQ_SCALE_PER_CHANNEL
     with pytest.raises(ValueError):
         scale_kind_for((5, 3), (3,))
+
+
+def test_split_streams_is_slicing_with_a_concatenating_backward():
+    """`harness.split_streams` (pure tensor ops, so it runs here): values equal the plain slices, outputs
+    are contiguous, and the gradient of any function of the two parts equals the one through slicing —
+    for one sample (bypass: views) and for several (one copy forward, one concatenation backward)."""
+    import torch
+
+    from loractl_b200.harness import split_streams
+
+    for b in (1, 3):
+        x = torch.randn(b, 7, 5, dtype=torch.float64, requires_grad=True)
+        y = x.detach().clone().requires_grad_(True)
+        img, txt = split_streams(x, 4)
+        assert img.is_contiguous() and txt.is_contiguous()
+        assert torch.equal(img, y[:, :4]) and torch.equal(txt, y[:, 4:])
+        w_img, w_txt = torch.randn(b, 4, 5, dtype=torch.float64), torch.randn(b, 3, 5, dtype=torch.float64)
+        ((img * w_img).sum() + (img ** 2).sum() + (txt * w_txt).sum()).backward()
+        ((y[:, :4] * w_img).sum() + (y[:, :4] ** 2).sum() + (y[:, 4:] * w_txt).sum()).backward()
+        assert torch.allclose(x.grad, y.grad, rtol=0, atol=1e-12)
